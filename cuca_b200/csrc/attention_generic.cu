@@ -16,7 +16,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const T* __restrict__ kpool, const T* __restrict__ vpool, int n_blocks, int bs,
                          const int* __restrict__ positions, const int* __restrict__ seq_of_row,
                          const int* __restrict__ tables, int table_stride, int nh, int nkv, int d, int dv,
-                         float scale, int window, int* err) {
+                         float scale, int window, float softcap, int sink, int* err) {
   extern __shared__ float qs[];  // [4][d]
   pdl_trigger();
   pdl_wait();
@@ -59,6 +59,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
       float dot = 0.f;
       for (int i = 0; i < d; ++i) dot = fmaf(qv[i], to_f32(kr[i]), dot);
       s = dot * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);  // a smooth cap on the score
     }
     float m_new = fmaxf(m, warp_max(s));
     if (m_new == -INFINITY) continue;  // a tile with no readable key
@@ -80,6 +81,13 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     }
     m = m_new;
   }
+  if (sink) {  // one more term in the denominator: a key of score 0 that has no value
+    const float m_new = fmaxf(m, 0.f);
+    const float corr = expf(m - m_new);
+    l = l * corr + expf(-m_new);
+#pragma unroll
+    for (int c = 0; c < VC; ++c) acc[c] *= corr;
+  }
   float inv = l > 0.f ? 1.f / l : 0.f;
   T* o = out + (size_t)row * out_stride + (size_t)head * dv;
 #pragma unroll
@@ -99,12 +107,13 @@ CUCA_API int cuca_attention_max_head_dim() { return 256; }
 // q: rows of `q_stride` elements whose first nh*d hold the (rotated) query
 // heads; out: [n_rows, out_stride] with nh heads of dv values; key pool [n_blocks][nkv][bs][d], value pool
 // [n_blocks][nkv][bs][dv]. Row r is at position positions[r] of sequence seq_of_row[r] (< 0: padding, skipped) and
-// sees keys max(0, P - window + 1)..P of that sequence (window 0: all).
-CUCA_API int cuca_attention_generic_v(const void* q, int q_stride, void* out, int out_stride, int dtype,
+// sees keys max(0, P - window + 1)..P of that sequence (window 0: all). softcap c > 0: a score s becomes
+// c tanh(s / c). sink: the softmax's denominator holds one more term, exp(0).
+CUCA_API int cuca_attention_generic_s(const void* q, int q_stride, void* out, int out_stride, int dtype,
                                       const void* kpool, const void* vpool, int n_blocks, int bs,
                                       const int* positions, const int* seq_of_row, const int* tables,
                                       int table_stride, int n_rows, int nh, int nkv, int d, int dv, float scale,
-                                      int window, int* err, cudaStream_t stream) {
+                                      int window, float softcap, int sink, int* err, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(d > 0 && d <= cuca_attention_max_head_dim(), "attention: head size %d is outside 1..%d", d, cuca_attention_max_head_dim());
   CUCA_REQUIRE(dv > 0 && dv <= 2 * cuca_attention_max_head_dim(), "attention: value size %d is outside 1..%d", dv,
@@ -116,7 +125,7 @@ CUCA_API int cuca_attention_generic_v(const void* q, int q_stride, void* out, in
 #define AG(T, VC)                                                                                                  \
   cuca_launch(attention_generic_kernel<T, VC>, grid, dim3(128), smem, stream, true, (const T*)q, q_stride, (T*)out, \
               out_stride, (const T*)kpool, (const T*)vpool, n_blocks, bs, positions, seq_of_row, tables,            \
-              table_stride, nh, nkv, d, dv, scale, window, err)
+              table_stride, nh, nkv, d, dv, scale, window, softcap, sink, err)
   if (dtype == CUCA_F32) {
     if (dv <= 256) AG(float, 8); else AG(float, 16);
   } else if (dtype == CUCA_BF16) {
@@ -127,6 +136,15 @@ CUCA_API int cuca_attention_generic_v(const void* q, int q_stride, void* out, in
 #undef AG
   CUCA_CHECK_LAUNCH("attention_generic");
   return 0;
+}
+
+CUCA_API int cuca_attention_generic_v(const void* q, int q_stride, void* out, int out_stride, int dtype,
+                                      const void* kpool, const void* vpool, int n_blocks, int bs,
+                                      const int* positions, const int* seq_of_row, const int* tables,
+                                      int table_stride, int n_rows, int nh, int nkv, int d, int dv, float scale,
+                                      int window, int* err, cudaStream_t stream) {
+  return cuca_attention_generic_s(q, q_stride, out, out_stride, dtype, kpool, vpool, n_blocks, bs, positions, seq_of_row,
+                                  tables, table_stride, n_rows, nh, nkv, d, dv, scale, window, 0.f, 0, err, stream);
 }
 
 CUCA_API int cuca_attention_generic(const void* q, int q_stride, void* out, int out_stride, int dtype,
@@ -226,5 +244,113 @@ CUCA_API int cuca_rope_store_general(void* qkv, int dtype, int ld, int k_col, in
   else
     CUCA_REQUIRE(false, "rope_store: unknown dtype %d", dtype);
   CUCA_CHECK_LAUNCH("rope_store_general");
+  return 0;
+}
+
+// ---------------------------------------------------------------- head norms, rotation and the paged write
+// As above, with norms per head in 32-bit before the rotation: a q head becomes q / rms(q) * q_norm (k alike with
+// k_norm; a null weight: no norm), and with v_norm a v head becomes v / rms(v) (no weight) before it is kept. T is the
+// rows' type (a 32-bit projection result may feed 16-bit pools: TP); q is written in place when q_out is null, else to
+// q_out [rows, nh d] of the pools' type. A warp per head.
+namespace {
+template <typename T, typename TP>
+__global__ void __launch_bounds__(256)
+norm_rope_store_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, TP* __restrict__ q_out,
+                       const int* __restrict__ positions, const int* __restrict__ seq_of_row,
+                       const int* __restrict__ tables, int table_stride, const float* __restrict__ cos_t,
+                       const float* __restrict__ sin_t, int table_rows, int rot, int pairs,
+                       const float* __restrict__ q_norm, const float* __restrict__ k_norm, int v_norm, float eps,
+                       TP* __restrict__ kpool, TP* __restrict__ vpool, int n_blocks, int bs, int nh, int nkv, int d, int dv,
+                       int v_split, int* err) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int seq = seq_of_row[row];
+  if (seq < 0) return;
+  const int pos = positions[row];
+  const int half = rot / 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  T* base = qkv + (size_t)row * ld;
+  long long page_row = -1;
+  if (nkv > 0) {
+    int blk = pos >= 0 ? tables[(size_t)seq * table_stride + pos / bs] : -1;
+    if (blk < 0 || blk >= n_blocks) {
+      if (threadIdx.x == 0 && err) atomicExch(err, CUCA_ERR_BLOCK_RANGE);
+    } else {
+      page_row = (long long)blk * nkv * bs + (pos % bs);
+    }
+  }
+  const bool in_table = pos >= 0 && pos < table_rows;
+  if (!in_table && half > 0 && threadIdx.x == 0 && err) atomicExch(err, CUCA_ERR_TOKEN_RANGE);
+  const float* cr = cos_t + (size_t)(in_table ? pos : 0) * half;
+  const float* sr = sin_t + (size_t)(in_table ? pos : 0) * half;
+  const long long slab_rows = (long long)n_blocks * nkv * bs;
+  for (int head = warp; head < nh + 2 * nkv; head += n_warps) {
+    const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
+    if (kind != 0 && page_row < 0) continue;
+    const int hh = kind == 0 ? head : (kind == 1 ? head - nh : head - nh - nkv);
+    const int n = kind == 2 ? dv : d;
+    const T* src = base + (kind == 0 ? 0 : (kind == 1 ? k_col : v_col)) + (size_t)hh * n;
+    const float* w = kind == 0 ? q_norm : (kind == 1 ? k_norm : nullptr);
+    const bool normed = kind == 2 ? v_norm != 0 : w != nullptr;
+    float inv = 1.f;
+    if (normed) {
+      float ss = 0.f;
+      for (int i = lane; i < n; i += 32) { const float v = to_f32(src[i]); ss = fmaf(v, v, ss); }
+      inv = 1.f / sqrtf(warp_sum(ss) / (float)n + eps);
+    }
+    __syncwarp();  // every lane has read the head before any lane rewrites it
+    if (kind == 2) {
+      const int ds = dv / v_split;
+      for (int e = lane; e < dv; e += 32)
+        vpool[((e / ds) * slab_rows + page_row + (long long)hh * bs) * ds + e % ds] = from_f32<TP>(to_f32(src[e]) * inv);
+      continue;
+    }
+    TP* dst_p = kind == 1 ? kpool + (page_row + (long long)hh * bs) * d
+                          : (q_out ? q_out + ((size_t)row * nh + hh) * d : nullptr);
+    T* dst_t = base + (size_t)hh * d;  // q in place
+    auto put = [&](int e, float v) {
+      if (dst_p) dst_p[e] = from_f32<TP>(v);
+      else dst_t[e] = from_f32<T>(v);
+    };
+    for (int i = lane; i < half + (d - rot); i += 32) {
+      if (i < half) {
+        const int ia = pairs ? 2 * i : i, ib = pairs ? 2 * i + 1 : i + half;
+        const float c = in_table ? cr[i] : 1.f, sn = in_table ? sr[i] : 0.f;
+        const float a = to_f32(src[ia]) * inv * (w ? w[ia] : 1.f), b = to_f32(src[ib]) * inv * (w ? w[ib] : 1.f);
+        put(ia, a * c - b * sn);
+        put(ib, b * c + a * sn);
+      } else {
+        const int e = rot + (i - half);
+        put(e, to_f32(src[e]) * inv * (w ? w[e] : 1.f));
+      }
+    }
+  }
+}
+}  // namespace
+
+// dtype: of the rows; pool_dtype: of the pools and of q_out (null: q in place, in the rows' type).
+CUCA_API int cuca_norm_rope_store(void* qkv, int dtype, int ld, int k_col, int v_col, void* q_out, int pool_dtype,
+                                  const int* positions, const int* seq_of_row, const int* tables, int table_stride,
+                                  const float* cos_t, const float* sin_t, int table_rows, int rot, int pairs,
+                                  const float* q_norm, const float* k_norm, int v_norm, float eps, void* kpool,
+                                  void* vpool, int n_blocks, int bs, int n_rows, int nh, int nkv, int d, int dv,
+                                  int v_split, int* err, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CUCA_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "norm_rope_store: rotary size %d does not fit head size %d", rot, d);
+  CUCA_REQUIRE(bs > 0 && nh > 0 && nkv >= 0 && d > 0 && dv > 0, "norm_rope_store: bad sizes");
+  CUCA_REQUIRE(v_split >= 1 && dv % v_split == 0, "norm_rope_store: %d slabs do not divide value size %d", v_split, dv);
+#define NRS(T, TP)                                                                                                    \
+  cuca_launch(norm_rope_store_kernel<T, TP>, dim3(n_rows), dim3(256), 0, stream, true, (T*)qkv, ld, k_col, v_col,      \
+              (TP*)q_out, positions, seq_of_row, tables, table_stride, cos_t, sin_t, table_rows, rot, pairs, q_norm,   \
+              k_norm, v_norm, eps, (TP*)kpool, (TP*)vpool, n_blocks, bs, nh, nkv, d, dv, v_split, err)
+  if (dtype == CUCA_F32 && pool_dtype == CUCA_F32) NRS(float, float);
+  else if (dtype == CUCA_BF16 && pool_dtype == CUCA_BF16) NRS(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == CUCA_F32 && pool_dtype == CUCA_BF16) {
+    CUCA_REQUIRE(q_out != nullptr, "norm_rope_store: 32-bit rows with 16-bit pools need a place for q");
+    NRS(float, __nv_bfloat16);
+  } else CUCA_REQUIRE(false, "norm_rope_store: unsupported dtypes %d/%d", dtype, pool_dtype);
+#undef NRS
+  CUCA_CHECK_LAUNCH("norm_rope_store");
   return 0;
 }

@@ -32,7 +32,7 @@ CUCA_API int cuca_set_pdl(int on) { g_pdl = on ? 1 : 0; return 0; }
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ x, int E, int V, int* err) {
+                             float* __restrict__ x, int E, int V, int* err, float scale) {
   pdl_trigger();
   pdl_wait();
   int row = blockIdx.x;
@@ -52,32 +52,39 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
       const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]), c = __bfloat1622float2(h[2]),
                    d = __bfloat1622float2(h[3]);
-      reinterpret_cast<float4*>(dst)[2 * i] = make_float4(a.x, a.y, b.x, b.y);
-      reinterpret_cast<float4*>(dst)[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+      reinterpret_cast<float4*>(dst)[2 * i] = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+      reinterpret_cast<float4*>(dst)[2 * i + 1] = make_float4(c.x * scale, c.y * scale, d.x * scale, d.y * scale);
     }
     return;
   }
   if (sizeof(T) == 4 && (E & 3) == 0 && (((size_t)src) & 15) == 0 && (((size_t)dst) & 15) == 0) {
-    for (int i = threadIdx.x; i < (E >> 2); i += blockDim.x)
-      reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(src)[i];
+    for (int i = threadIdx.x; i < (E >> 2); i += blockDim.x) {
+      const float4 v = reinterpret_cast<const float4*>(src)[i];
+      reinterpret_cast<float4*>(dst)[i] = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
+    }
     return;
   }
-  for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = to_f32(src[i]);
+  for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = to_f32(src[i]) * scale;
 }
 
-// Embedding rows of `tokens[n_rows]` into the 32-bit stream x[n_rows, E].
-CUCA_API int cuca_embed(const void* table, int table_dtype, const int* tokens, float* x,
-                        int n_rows, int E, int V, int* err, cudaStream_t stream) {
+// Embedding rows of `tokens[n_rows]`, times `scale`, into the 32-bit stream x[n_rows, E].
+CUCA_API int cuca_embed_scaled(const void* table, int table_dtype, const int* tokens, float* x,
+                               int n_rows, int E, int V, float scale, int* err, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(E > 0 && V > 0, "embed: bad sizes E=%d V=%d", E, V);
   if (table_dtype == CUCA_F32)
-    embed_kernel<float><<<n_rows, 256, 0, stream>>>((const float*)table, tokens, x, E, V, err);
+    embed_kernel<float><<<n_rows, 256, 0, stream>>>((const float*)table, tokens, x, E, V, err, scale);
   else if (table_dtype == CUCA_BF16)
-    embed_kernel<__nv_bfloat16><<<n_rows, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, E, V, err);
+    embed_kernel<__nv_bfloat16><<<n_rows, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, E, V, err, scale);
   else
     CUCA_REQUIRE(false, "embed: unknown dtype %d", table_dtype);
   CUCA_CHECK_LAUNCH("embed");
   return 0;
+}
+
+CUCA_API int cuca_embed(const void* table, int table_dtype, const int* tokens, float* x,
+                        int n_rows, int E, int V, int* err, cudaStream_t stream) {
+  return cuca_embed_scaled(table, table_dtype, tokens, x, n_rows, E, V, 1.f, err, stream);
 }
 
 // ---------------------------------------------------------------- RMSNorm
@@ -120,16 +127,21 @@ __device__ __forceinline__ void store4(__nv_bfloat16* o, float a, float b, float
 template <typename TW, typename TO, bool PARTIAL, int VL>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ partial, int n_slices,
                                size_t slice_stride, const TW* __restrict__ w, TO* __restrict__ out,
-                               const int* __restrict__ rows, int E, float eps) {
+                               const int* __restrict__ rows, int E, float eps, int groups) {
   __shared__ float red[32];
   pdl_trigger();
   pdl_wait();
-  int orow = blockIdx.x;
+  // `groups` equal consecutive parts of a row are normed apart: a block takes one part of E values (the row is
+  // groups * E wide), so a part's arithmetic is that of a whole row of its width
+  int orow = blockIdx.x, part = 0;
+  if (groups > 1) { part = orow % groups; orow /= groups; }
   int irow = rows ? rows[orow] : orow;
   if (irow < 0) return;
-  float* xr = x + (size_t)irow * E;
-  const float* pr = PARTIAL ? partial + (size_t)irow * E : nullptr;
-  TO* o = out + (size_t)orow * E;
+  const size_t ld = (size_t)E * groups;
+  float* xr = x + (size_t)irow * ld + (size_t)part * E;
+  const float* pr = PARTIAL ? partial + (size_t)irow * ld + (size_t)part * E : nullptr;
+  TO* o = out + (size_t)orow * ld + (size_t)part * E;
+  w += (size_t)part * E;
   float s = 0.f;
   const bool vec = (E & 3) == 0 && (((size_t)xr) & 15) == 0 && (!PARTIAL || ((((size_t)pr) | (slice_stride * 4)) & 15) == 0);
   if (vec) {
@@ -203,11 +215,15 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
   }
 }
 
-// out[r] = x[rows ? rows[r] : r] * rsqrt(mean(x^2) + eps) * w
-CUCA_API int cuca_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
-                          const int* rows, int n_rows, int E, float eps, cudaStream_t stream) {
+// out[r] = x[rows ? rows[r] : r] * rsqrt(mean(x^2) + eps) * w; with groups > 1 every one of `groups` equal consecutive
+// parts of a row is divided by its own root mean square.
+CUCA_API int cuca_rmsnorm_groups(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
+                                 const int* rows, int n_rows, int E, float eps, int groups, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  CUCA_REQUIRE(E > 0, "rmsnorm: bad width %d", E);
+  CUCA_REQUIRE(E > 0 && groups >= 1 && E % groups == 0, "rmsnorm: %d parts do not divide the width %d", groups, E);
+  CUCA_REQUIRE((long long)n_rows * groups < (1ll << 31), "rmsnorm: %d rows of %d parts exceed the launch limit", n_rows, groups);
+  E /= groups;
+  n_rows *= groups;
   float* xm = const_cast<float*>(x);  // not written without PARTIAL
   // many rows: a quarter of the threads per block, four value groups each (bit-equal to the wide block)
   const bool narrow = norm_block(E) == 1024 && n_rows >= 64 && (E & 3) == 0;
@@ -215,10 +231,10 @@ CUCA_API int cuca_rmsnorm(const float* x, const void* w, int w_dtype, void* out,
   do {                                                                                                          \
     if (narrow)                                                                                                 \
       cuca_launch(rmsnorm_kernel<TW, TO, false, 4>, dim3(n_rows), dim3(256), 0, stream, true, xm,               \
-                  (const float*)nullptr, 0, (size_t)0, (const TW*)w, (TO*)out, rows, E, eps);                   \
+                  (const float*)nullptr, 0, (size_t)0, (const TW*)w, (TO*)out, rows, E, eps, groups);           \
     else                                                                                                        \
       cuca_launch(rmsnorm_kernel<TW, TO, false, 1>, dim3(n_rows), dim3(norm_block(E)), 0, stream, true, xm,     \
-                  (const float*)nullptr, 0, (size_t)0, (const TW*)w, (TO*)out, rows, E, eps);                   \
+                  (const float*)nullptr, 0, (size_t)0, (const TW*)w, (TO*)out, rows, E, eps, groups);           \
   } while (0)
   if (w_dtype == CUCA_F32 && out_dtype == CUCA_F32) LAUNCH(float, float);
   else if (w_dtype == CUCA_F32 && out_dtype == CUCA_BF16) LAUNCH(float, __nv_bfloat16);
@@ -228,6 +244,11 @@ CUCA_API int cuca_rmsnorm(const float* x, const void* w, int w_dtype, void* out,
 #undef LAUNCH
   CUCA_CHECK_LAUNCH("rmsnorm");
   return 0;
+}
+
+CUCA_API int cuca_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
+                          const int* rows, int n_rows, int E, float eps, cudaStream_t stream) {
+  return cuca_rmsnorm_groups(x, w, w_dtype, out, out_dtype, rows, n_rows, E, eps, 1, stream);
 }
 
 // ---------------------------------------------------------------- rotary + paged K/V write
@@ -421,6 +442,41 @@ CUCA_API int cuca_swiglu(const void* gu, void* out, int dtype, int n_rows, int f
   return 0;
 }
 
+// ---------------------------------------------------------------- a gated unit with capped inputs
+// out[r, j] = g sigmoid(alpha g) (u + 1) with g = min(gu[r, j], limit), u = clamp(gu[r, ff + j], -limit, limit)
+template <typename T>
+__global__ void glu_capped_kernel(const T* __restrict__ gu, T* __restrict__ out, int ff, size_t total, float limit,
+                                  float alpha) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / ff;
+    const int j = (int)(i % ff);
+    const float g = fminf(to_f32(gu[r * 2 * ff + j]), limit);
+    const float u = fminf(fmaxf(to_f32(gu[r * 2 * ff + ff + j]), -limit), limit);
+    out[i] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+  }
+}
+
+CUCA_API int cuca_glu_capped(const void* gu, void* out, int dtype, int n_rows, int ff, float limit, float alpha,
+                             cudaStream_t stream) {
+  const size_t total = (size_t)n_rows * ff;
+  if (total == 0) return 0;
+  CUCA_REQUIRE(limit > 0.f, "glu_capped: the cap %g must be positive", (double)limit);
+  size_t blocks = (total + 255) / 256;
+  blocks = blocks > 16384 ? 16384 : blocks;
+  if (dtype == CUCA_F32)
+    cuca_launch(glu_capped_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, true, (const float*)gu,
+                (float*)out, ff, total, limit, alpha);
+  else if (dtype == CUCA_BF16)
+    cuca_launch(glu_capped_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, true,
+                (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, ff, total, limit, alpha);
+  else
+    CUCA_REQUIRE(false, "glu_capped: unknown dtype %d", dtype);
+  CUCA_CHECK_LAUNCH("glu_capped");
+  return 0;
+}
+
 // ---------------------------------------------------------------- stream += delta
 template <typename T>
 __global__ void add_kernel(float* __restrict__ x, const T* __restrict__ delta, size_t total) {
@@ -459,21 +515,30 @@ CUCA_API int cuca_scatter_int(int* dst, const int* idx, const int* val, int n, l
 // 32-bit sums, and the next kernel, which reads every value anyway, adds them in slice order.
 
 // x[row] += sum over slices; out[orow] = RMSNorm(x[row]) * w (the RMSNorm kernel above with PARTIAL).
-CUCA_API int cuca_add_partials_rmsnorm(float* x, const float* partial, int n_slices, size_t slice_stride,
-                                       const float* w, void* out, int out_dtype, const int* rows, int n_rows, int E,
-                                       float eps, cudaStream_t stream) {
+CUCA_API int cuca_add_partials_rmsnorm_groups(float* x, const float* partial, int n_slices, size_t slice_stride,
+                                              const float* w, void* out, int out_dtype, const int* rows, int n_rows,
+                                              int E, float eps, int groups, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  CUCA_REQUIRE(E > 0 && n_slices >= 1, "add_partials_rmsnorm: bad sizes");
+  CUCA_REQUIRE(E > 0 && n_slices >= 1 && groups >= 1 && E % groups == 0, "add_partials_rmsnorm: bad sizes");
+  E /= groups;
+  n_rows *= groups;
   if (out_dtype == CUCA_BF16)
     cuca_launch(rmsnorm_kernel<float, __nv_bfloat16, true, 1>, dim3(n_rows), dim3(norm_block(E)), 0, stream, true, x,
-                partial, n_slices, slice_stride, w, (__nv_bfloat16*)out, rows, E, eps);
+                partial, n_slices, slice_stride, w, (__nv_bfloat16*)out, rows, E, eps, groups);
   else if (out_dtype == CUCA_F32)
     cuca_launch(rmsnorm_kernel<float, float, true, 1>, dim3(n_rows), dim3(norm_block(E)), 0, stream, true, x, partial,
-                n_slices, slice_stride, w, (float*)out, rows, E, eps);
+                n_slices, slice_stride, w, (float*)out, rows, E, eps, groups);
   else
     CUCA_REQUIRE(false, "add_partials_rmsnorm: unknown dtype %d", out_dtype);
   CUCA_CHECK_LAUNCH("add_partials_rmsnorm");
   return 0;
+}
+
+CUCA_API int cuca_add_partials_rmsnorm(float* x, const float* partial, int n_slices, size_t slice_stride,
+                                       const float* w, void* out, int out_dtype, const int* rows, int n_rows, int E,
+                                       float eps, cudaStream_t stream) {
+  return cuca_add_partials_rmsnorm_groups(x, partial, n_slices, slice_stride, w, out, out_dtype, rows, n_rows, E, eps, 1,
+                                          stream);
 }
 
 // x += sum over slices: for a reader of the stream that does not add the slices itself.

@@ -4,6 +4,8 @@
 //   mlstm_scan      a matrix memory with exponential gates and a running maximum m (0 at the start):
 //                     m' = max(f + m, i);  S <- e^(f + m - m') S + e^(i - m') k v^T;  n likewise from k alone;
 //                     o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)
+//   forget_scan     linear attention whose forget gate f (per key channel) is also one minus its write strength:
+//                     S <- f * S (rows) + (1 - f) v^T;  o = S^T q
 //   head_norm_gate  out = o / rms(o) per head, times a weight, times sigmoid(gate)
 // What does not depend on the state (unit vectors, decays, gates) is computed for all rows at once by a preparing
 // kernel, in place. A scan block then takes one (head, request, run of value columns) and walks the request's rows of
@@ -173,6 +175,114 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const f
         const float4 qv = gq[i];
         S[4 * i] = fmaf(kk[4 * i], u, S[4 * i]); S[4 * i + 1] = fmaf(kk[4 * i + 1], u, S[4 * i + 1]);
         S[4 * i + 2] = fmaf(kk[4 * i + 2], u, S[4 * i + 2]); S[4 * i + 3] = fmaf(kk[4 * i + 3], u, S[4 * i + 3]);
+        p0 = fmaf(S[4 * i], qv.x, p0); p1 = fmaf(S[4 * i + 1], qv.y, p1);
+        p2 = fmaf(S[4 * i + 2], qv.z, p2); p3 = fmaf(S[4 * i + 3], qv.w, p3);
+      }
+      const float po = group_sum((p0 + p1) + (p2 + p3), NS);
+      if (s == 0 && live) *po_at = po;
+    }
+    __syncthreads();  // the buffer is free for the copies of the chunk after next
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NR; ++i)
+      if (s * NR + i < d) st[s * NR + i] = S[i];
+  }
+}
+
+// Per row, in place, of a 32-bit projection [q | f | ...]: q (H d values at q_col) becomes silu(q); the forget gate's
+// pre-activation (H d values at f_col) becomes f = l + (1 - l) sigmoid(x + bias) with a lower bound l per channel.
+__global__ void forget_prepare_kernel(float* __restrict__ proj, int ld, int q_col, int f_col,
+                                      const float* __restrict__ f_bias, const float* __restrict__ lower,
+                                      const int* __restrict__ seq_of_row, int n_rows, int n) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < (size_t)n_rows * n; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = e / n;
+    const int i = (int)(e % n);
+    if (seq_of_row[row] < 0) continue;
+    float* r = proj + row * ld;
+    const float q = r[q_col + i];
+    r[q_col + i] = q * sigmoidf_(q);
+    const float l = lower[i];
+    r[f_col + i] = l + (1.f - l) * sigmoidf_(r[f_col + i] + (f_bias ? f_bias[i] : 0.f));
+  }
+}
+
+// proj: 32-bit rows of stride ld, prepared: q heads at q_col (H heads of d), forget gates at f_col (H heads of d),
+// v heads at v_col (H heads of dv). state: [slots, H, dv, d]. out: [rows, H dv]. The delta scan's sibling without a
+// correction: one shuffled sum per token and column.
+template <int NR>
+__global__ void forget_scan_kernel(const float* __restrict__ proj, int ld, int q_col, int f_col, int v_col,
+                                   float* __restrict__ state, float* __restrict__ out,
+                                   const int* __restrict__ req_row0, const int* __restrict__ req_count,
+                                   const int* __restrict__ slots, int H, int d, int dv, int NS, int PB, int TC, int wide) {
+  extern __shared__ __align__(16) float sm[];
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.x, rq = blockIdx.y;
+  const int slot = slots[rq], n = req_count[rq], r0 = req_row0[rq];
+  if (slot < 0 || n <= 0) return;
+  const int dpp = NS * staged_stride<NR>();  // a staged vector with its padding
+  const int per = (2 * dpp + PB + 3) & ~3;   // a token: q, f, the block's values
+  const int col_local = threadIdx.x / NS, s = threadIdx.x % NS;
+  const int col = blockIdx.z * PB + col_local;
+  const bool live = col_local < PB && col < dv;
+  float S[NR];
+  float* st = state + (((size_t)slot * H + h) * dv + (live ? col : 0)) * d;
+#pragma unroll
+  for (int i = 0; i < NR; ++i) S[i] = (live && s * NR + i < d) ? st[s * NR + i] : 0.f;
+  // what no copy writes: channels from d on (q = 0, f = 1) and the values of columns from dv on
+  {
+    const int spare = NS * NR - d, fill = 2 * spare + PB;
+    for (int e = threadIdx.x; e < 2 * TC * fill; e += blockDim.x) {
+      const int t = e / fill, w = e % fill;
+      float* tok = sm + (size_t)t * per;
+      if (w < 2 * spare) tok[(w / spare) * dpp + staged_at<NR>(d + w % spare)] = w / spare == 1 ? 1.f : 0.f;
+      else tok[2 * dpp + (w - 2 * spare)] = 0.f;
+    }
+  }
+  __syncthreads();
+  auto stage = [&](int t0, int buf) {
+    const int nt = n - t0 < TC ? n - t0 : TC;
+    float* base = sm + (size_t)buf * TC * per;
+    const int step = wide ? 4 : 1, units = d / step;
+    for (int e = threadIdx.x; e < nt * 2 * units; e += blockDim.x) {
+      const int t = e / (2 * units), u = e % (2 * units), which = u / units, r = (u % units) * step;
+      const float* src = proj + (size_t)(r0 + t0 + t) * ld + (which ? f_col : q_col) + (size_t)h * d + r;
+      cp_async_f(base + (size_t)t * per + which * dpp + staged_at<NR>(r), src, wide);
+    }
+    for (int e = threadIdx.x; e < nt * PB; e += blockDim.x) {
+      const int t = e / PB, i = e % PB;
+      if (blockIdx.z * PB + i < dv)
+        cp_async_f(base + (size_t)t * per + 2 * dpp + i,
+                   proj + (size_t)(r0 + t0 + t) * ld + v_col + (size_t)h * dv + blockIdx.z * PB + i, false);
+    }
+    cp_async_commit();
+  };
+  const int cv = col_local < PB ? col_local : PB - 1;
+  const int n_chunks = (n + TC - 1) / TC;
+  stage(0, 0);
+  for (int c = 0; c < n_chunks; ++c) {
+    if (c + 1 < n_chunks) { stage((c + 1) * TC, (c + 1) & 1); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
+    __syncthreads();
+    const int t0 = c * TC, nt = n - t0 < TC ? n - t0 : TC;
+    const float* tok = sm + (size_t)(c & 1) * TC * per;
+    float* po_at = out + (size_t)(r0 + t0) * H * dv + (size_t)h * dv + col;
+    const int mine = s * staged_stride<NR>();
+#pragma unroll 2
+    for (int t = 0; t < nt; ++t, tok += per, po_at += H * dv) {
+      const float4* gq = reinterpret_cast<const float4*>(tok + mine);
+      const float4* gf = reinterpret_cast<const float4*>(tok + dpp + mine);
+      const float v = tok[2 * dpp + cv];
+      float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < NR / 4; ++i) {
+        const float4 f4 = gf[i], qv = gq[i];
+        // f S + (1 - f) v, each product rounded as the plain recurrence rounds it
+        S[4 * i] = fmaf(f4.x, S[4 * i], (1.f - f4.x) * v); S[4 * i + 1] = fmaf(f4.y, S[4 * i + 1], (1.f - f4.y) * v);
+        S[4 * i + 2] = fmaf(f4.z, S[4 * i + 2], (1.f - f4.z) * v); S[4 * i + 3] = fmaf(f4.w, S[4 * i + 3], (1.f - f4.w) * v);
         p0 = fmaf(S[4 * i], qv.x, p0); p1 = fmaf(S[4 * i + 1], qv.y, p1);
         p2 = fmaf(S[4 * i + 2], qv.z, p2); p3 = fmaf(S[4 * i + 3], qv.w, p3);
       }
@@ -489,6 +599,45 @@ CUCA_API int cuca_mlstm_scan(float* proj, int ld, int q_col, int k_col, int v_co
   cuca_launch(mlstm_commit_kernel, dim3(H, n_seqs), dim3(128), 0, stream, true, (const float*)nm_new, nrm, mx, req_count,
               slots, H, d);
   CUCA_CHECK_LAUNCH("mlstm_commit");
+  return 0;
+}
+
+// The q and forget-gate columns of proj are rewritten in place by the preparing kernel (see there), then scanned.
+CUCA_API int cuca_forget_scan(float* proj, int ld, int q_col, int f_col, int v_col, const float* f_bias,
+                              const float* lower, float* state, float* out, const int* seq_of_row, const int* req_row0,
+                              const int* req_count, const int* slots, int n_rows, int n_seqs, int H, int d, int dv,
+                              cudaStream_t stream) {
+  if (n_seqs == 0 || n_rows == 0) return 0;
+  CUCA_REQUIRE(H > 0 && d > 0 && dv > 0, "forget_scan: bad sizes heads=%d dim=%d vdim=%d", H, d, dv);
+  CUCA_REQUIRE(n_seqs <= 65535, "forget_scan: %d requests exceed the launch limit", n_seqs);
+  int ns, nr;
+  CUCA_REQUIRE(split_rows(d, (long long)n_seqs * H * dv, &ns, &nr), "forget_scan: %d key channels exceed %d", d, 32 * MAXR);
+  {
+    size_t blocks = ((size_t)n_rows * H * d + 255) / 256;
+    blocks = blocks > 8192 ? 8192 : blocks;
+    cuca_launch(forget_prepare_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, true, proj, ld, q_col, f_col, f_bias,
+                lower, seq_of_row, n_rows, H * d);
+    CUCA_CHECK_LAUNCH("forget_prepare");
+  }
+  int pb = block_threads(ns, nr) / ns;
+  pb = pb > dv ? dv : pb;
+  const int threads = (pb * ns + 31) / 32 * 32;
+  const int per = (2 * ns * (nr == 4 ? 4 : nr + 4) + pb + 3) & ~3;
+  int tc = 46000 / (2 * per * 4);
+  tc = tc > 16 ? 16 : tc;
+  CUCA_REQUIRE(tc >= 1, "forget_scan: a token of %d key channels does not fit shared memory", d);
+  const size_t smem = (size_t)2 * tc * per * 4;
+  const int wide = d % 4 == 0 && ld % 4 == 0 && q_col % 4 == 0 && f_col % 4 == 0 && ((uintptr_t)proj & 15) == 0;
+  dim3 grid(H, n_seqs, (dv + pb - 1) / pb);
+#define FS(NR)                                                                                                     \
+  cuca_launch(forget_scan_kernel<NR>, grid, dim3(threads), smem, stream, true, (const float*)proj, ld, q_col, f_col, \
+              v_col, state, out, req_row0, req_count, slots, H, d, dv, ns, pb, tc, wide)
+  if (nr == 4) FS(4);
+  else if (nr == 8) FS(8);
+  else if (nr == 16) FS(16);
+  else FS(32);
+#undef FS
+  CUCA_CHECK_LAUNCH("forget_scan");
   return 0;
 }
 

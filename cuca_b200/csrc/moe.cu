@@ -4,6 +4,11 @@
 //   moe_act_dense    a[t, e, f] = relu(u[t, e, f])^2 * weight[t, e]: all experts' up-projections at once, the ones a
 //                    token did not choose weighted 0, so that one contraction over (e, f) is the weighted sum
 //   moe_up_sparse / moe_down_sparse   few tokens: only the chosen experts' weights are read, a warp per output
+//   moe_route_scored scores are a softmax over ALL router outputs; the choice goes by score + a correction per output,
+//                    the weights are the chosen scores over their sum; the last outputs may stand for experts that
+//                    return their input (their weights are summed per token for `moe_identity_add`)
+//   moe_glu_dense    a[t, c] = silu(g[t, c]) u[t, c] * weight[t, expert of c]: gated experts, and behind them the
+//                    columns of a shared expert that every token uses with weight 1
 // Routing arithmetic is 32-bit. A token's experts are summed in a fixed order, whatever else is in the batch.
 #include "common.cuh"
 #include <math.h>
@@ -69,6 +74,98 @@ __global__ void moe_act_dense_kernel(const T* __restrict__ u, const float* __res
   }
 }
 
+// Scores over all E router outputs; `top` chosen by score + correction (the lower number on a tie); weights
+// s / (sum of the chosen s + 1e-20). Outputs from n_real on are identity experts: their chosen weights are summed in
+// ident[t]. A warp per token; lane l holds outputs l, l + 32, ...
+__global__ void __launch_bounds__(128)
+moe_route_scored_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int T, int E, int n_real,
+                        int top, int* __restrict__ idx, float* __restrict__ wts, float* __restrict__ dense,
+                        float* __restrict__ ident) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const float* z = logits + (size_t)t * E;
+  float zmax = -INFINITY;
+  for (int e = lane; e < E; e += 32) {
+    const float v = z[e];
+    zmax = fmaxf(zmax, v == v ? v : -INFINITY);
+  }
+  zmax = warp_max(zmax);
+  if (zmax == -INFINITY) zmax = 0.f;  // a row of padding may hold anything
+  float total = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float v = z[e];
+    total += v == v ? expf(v - zmax) : 0.f;
+  }
+  total = warp_sum(total);
+  const float inv_total = total > 0.f ? 1.f / total : 0.f;
+  unsigned taken = 0;
+  float my_s = 0.f;
+  int my_e = 0;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY, best_s = 0.f;
+    int be = 0x7fffffff;
+    for (int k = 0; lane + 32 * k < E; ++k) {
+      const int e = lane + 32 * k;
+      const float v = z[e];
+      const float sc = v == v ? expf(v - zmax) * inv_total : 0.f;
+      float c = sc + (correction ? correction[e] : 0.f);
+      c = c == c ? c : -INFINITY;
+      if (!((taken >> k) & 1u) && (c > best || (c == best && e < be) || be == 0x7fffffff)) { best = c; be = e; best_s = sc; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (oe != 0x7fffffff && (be == 0x7fffffff || ov > best || (ov == best && oe < be))) { best = ov; be = oe; best_s = os; }
+    }
+    if (be < E && (be & 31) == lane) taken |= 1u << (be >> 5);
+    if (lane == j) { my_s = best_s; my_e = be < E ? be : 0; }
+  }
+  const float chosen = warp_sum(lane < top ? my_s : 0.f);
+  const float w = my_s / (chosen + 1e-20f);
+  const float iw = warp_sum(lane < top && my_e >= n_real ? w : 0.f);
+  if (dense)
+    for (int e = lane; e < E; e += 32) dense[(size_t)t * E + e] = 0.f;
+  __syncwarp();
+  if (lane < top) {
+    idx[(size_t)t * top + lane] = my_e;
+    wts[(size_t)t * top + lane] = w;
+    if (dense) dense[(size_t)t * E + my_e] = w;
+  }
+  if (ident && lane == 0) ident[t] = iw;
+}
+
+// gu: [T, 2 C] (gates, then ups); a[t, c] = silu(g) u w with w = dense[t, c / F] for c < EF (ld_dense outputs a row),
+// 1 for the columns behind (a shared expert).
+template <typename T>
+__global__ void moe_glu_dense_kernel(const T* __restrict__ gu, const float* __restrict__ dense, int ld_dense,
+                                     T* __restrict__ a, size_t n, int C, int EF, int F) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / C;
+    const int c = (int)(i % C);
+    const float w = c < EF ? dense[t * ld_dense + c / F] : 1.f;
+    const float g = to_f32(gu[t * 2 * C + c]), u = to_f32(gu[t * 2 * C + C + c]);
+    a[i] = from_f32<T>(w == 0.f ? 0.f : g / (1.f + expf(-g)) * u * w);
+  }
+}
+
+// y[t] (+)= ident[t] * h[t]: the experts that return their input.
+template <typename T>
+__global__ void moe_identity_add_kernel(float* __restrict__ y, const T* __restrict__ h, const float* __restrict__ ident,
+                                        int store, size_t n, int N) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = ident[i / N] * to_f32(h[i]);
+    y[i] = store ? v : y[i] + v;
+  }
+}
+
 // A warp's dot product of two rows of n values: 16 bytes a lane at a time where the rows allow it.
 __device__ __forceinline__ float warp_dot(const float* w, const float* x, int n, int lane) {
   float acc = 0.f;
@@ -95,30 +192,38 @@ __device__ __forceinline__ float warp_dot(const __nv_bfloat16* w, const __nv_bfl
   return warp_sum(acc);
 }
 
-// a[pair, f] = relu(W_up[e(pair)][f] . h[t])^2 * weight(pair); pair = t * top + j. W_up: [E F, K].
-template <typename T>
+// a[pair, f] = act(W[e(pair)] . h[t]) * weight(pair); pair = t * top + j. GLU false: W_up [E F, K], act = relu(.)^2.
+// GLU true: w_up holds every expert's gate rows and, `up_rows` rows further on, its up rows; act = silu(gate) up.
+// A pair whose expert number is n_real or more has no weights (it returns its input): nothing is written for it.
+template <typename T, bool GLU>
 __global__ void __launch_bounds__(256)
 moe_up_sparse_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __restrict__ idx,
-                     const float* __restrict__ wts, T* __restrict__ a, int top, int F, int K) {
+                     const float* __restrict__ wts, T* __restrict__ a, int top, int F, int K, int n_real, size_t up_rows) {
   pdl_trigger();
   pdl_wait();
   const int pair = blockIdx.y, f = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (f >= F) return;
   const int e = idx[pair];
+  if (e >= n_real) return;
   const T* wr = w_up + ((size_t)e * F + f) * K;
   const T* hr = h + (size_t)(pair / top) * K;
   const float acc = warp_dot(wr, hr, K, lane);
-  if (lane == 0) {
-    const float v = fmaxf(acc, 0.f);
-    a[(size_t)pair * F + f] = from_f32<T>(v * v * wts[pair]);
+  float v;
+  if (GLU) {
+    const float u = warp_dot(wr + up_rows * K, hr, K, lane);
+    v = acc / (1.f + expf(-acc)) * u;
+  } else {
+    v = fmaxf(acc, 0.f);
+    v = v * v;
   }
+  if (lane == 0) a[(size_t)pair * F + f] = from_f32<T>(v * wts[pair]);
 }
 
-// y[t, o] (+)= sum_j W_down[o, e(t, j) F ..] . a[t * top + j]; W_down: [N, E F]
+// y[t, o] (+)= sum_j W_down[o, e(t, j) F ..] . a[t * top + j]; W_down: [N, ld] (ld columns a row)
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_down_sparse_kernel(const T* __restrict__ a, const T* __restrict__ w_down, const int* __restrict__ idx,
-                       float* __restrict__ y, int store, int top, int F, int E, int N) {
+                       float* __restrict__ y, int store, int top, int F, int ld, int N, int n_real) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.y, o = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -126,7 +231,8 @@ moe_down_sparse_kernel(const T* __restrict__ a, const T* __restrict__ w_down, co
   float acc = 0.f;
   for (int j = 0; j < top; ++j) {
     const int e = idx[(size_t)t * top + j];
-    const T* wr = w_down + (size_t)o * E * F + (size_t)e * F;
+    if (e >= n_real) continue;
+    const T* wr = w_down + (size_t)o * ld + (size_t)e * F;
     const T* ar = a + ((size_t)t * top + j) * F;
     acc += warp_dot(wr, ar, F, lane);
   }
@@ -166,26 +272,81 @@ CUCA_API int cuca_moe_act_dense(const void* u, const float* dense, void* a, int 
   return 0;
 }
 
+// glu 0: relu(up)^2 experts, w_up [E F, K], w_down [N, E F]. glu 1: gated experts, w_up [2 C, K] (every expert's gate
+// rows, then C rows on every expert's up rows), w_down [N, C]; C >= E F (what lies behind belongs to a shared expert,
+// which this launch leaves alone). Pairs that name expert E or more are skipped.
 CUCA_API int cuca_moe_sparse(const void* h, const void* w_up, const void* w_down, const int* idx, const float* wts,
                              void* a, float* y, int store, int dtype, int T, int top, int E, int F, int K, int N,
-                             cudaStream_t stream) {
+                             int glu, int C, cudaStream_t stream) {
   if (T == 0) return 0;
   CUCA_REQUIRE(T * top <= 65535 && T <= 65535, "moe_sparse: %d tokens exceed the launch limit", T);
-  if (dtype == CUCA_F32) {
-    cuca_launch(moe_up_sparse_kernel<float>, dim3((F + 7) / 8, T * top), dim3(256), 0, stream, true, (const float*)h,
-                (const float*)w_up, idx, wts, (float*)a, top, F, K);
-    CUCA_CHECK_LAUNCH("moe_up_sparse");
-    cuca_launch(moe_down_sparse_kernel<float>, dim3((N + 7) / 8, T), dim3(256), 0, stream, true, (const float*)a,
-                (const float*)w_down, idx, y, store, top, F, E, N);
-  } else if (dtype == CUCA_BF16) {
-    cuca_launch(moe_up_sparse_kernel<__nv_bfloat16>, dim3((F + 7) / 8, T * top), dim3(256), 0, stream, true,
-                (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_up, idx, wts, (__nv_bfloat16*)a, top, F, K);
-    CUCA_CHECK_LAUNCH("moe_up_sparse");
-    cuca_launch(moe_down_sparse_kernel<__nv_bfloat16>, dim3((N + 7) / 8, T), dim3(256), 0, stream, true,
-                (const __nv_bfloat16*)a, (const __nv_bfloat16*)w_down, idx, y, store, top, F, E, N);
-  } else {
-    CUCA_REQUIRE(false, "moe_sparse: unknown dtype %d", dtype);
-  }
+  const int ld = glu ? C : E * F;
+  CUCA_REQUIRE(ld >= E * F, "moe_sparse: %d columns do not hold %d experts of %d", ld, E, F);
+#define SPARSE(TT)                                                                                                  \
+  do {                                                                                                              \
+    if (glu)                                                                                                        \
+      cuca_launch(moe_up_sparse_kernel<TT, true>, dim3((F + 7) / 8, T * top), dim3(256), 0, stream, true,           \
+                  (const TT*)h, (const TT*)w_up, idx, wts, (TT*)a, top, F, K, E, (size_t)C);                        \
+    else                                                                                                            \
+      cuca_launch(moe_up_sparse_kernel<TT, false>, dim3((F + 7) / 8, T * top), dim3(256), 0, stream, true,          \
+                  (const TT*)h, (const TT*)w_up, idx, wts, (TT*)a, top, F, K, E, (size_t)0);                        \
+    CUCA_CHECK_LAUNCH("moe_up_sparse");                                                                             \
+    cuca_launch(moe_down_sparse_kernel<TT>, dim3((N + 7) / 8, T), dim3(256), 0, stream, true, (const TT*)a,         \
+                (const TT*)w_down, idx, y, store, top, F, ld, N, E);                                                \
+  } while (0)
+  if (dtype == CUCA_F32) SPARSE(float);
+  else if (dtype == CUCA_BF16) SPARSE(__nv_bfloat16);
+  else CUCA_REQUIRE(false, "moe_sparse: unknown dtype %d", dtype);
+#undef SPARSE
   CUCA_CHECK_LAUNCH("moe_down_sparse");
+  return 0;
+}
+
+CUCA_API int cuca_moe_route_scored(const float* logits, const float* correction, int T, int E, int n_real, int top,
+                                   int* idx, float* wts, float* dense, float* ident, cudaStream_t stream) {
+  if (T == 0) return 0;
+  CUCA_REQUIRE(E >= 1 && E <= MAX_EXPERTS && top >= 1 && top <= E && top <= MAX_TOP && n_real >= 0 && n_real <= E,
+               "moe_route: %d of %d experts (%d with weights) is outside what the kernel takes (experts <= %d, "
+               "chosen <= %d)", top, E, n_real, MAX_EXPERTS, MAX_TOP);
+  cuca_launch(moe_route_scored_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, true, logits, correction, T, E, n_real,
+              top, idx, wts, dense, ident);
+  CUCA_CHECK_LAUNCH("moe_route_scored");
+  return 0;
+}
+
+CUCA_API int cuca_moe_glu_dense(const void* gu, const float* dense, int ld_dense, void* a, int dtype, int T, int C,
+                                int EF, int F, cudaStream_t stream) {
+  if (T == 0) return 0;
+  CUCA_REQUIRE(F >= 1 && EF % F == 0 && EF <= C && EF / F <= ld_dense, "moe_glu_dense: bad sizes C=%d EF=%d F=%d", C, EF, F);
+  const size_t n = (size_t)T * C;
+  size_t blocks = (n + 255) / 256;
+  blocks = blocks > 8192 ? 8192 : blocks;
+  if (dtype == CUCA_F32)
+    cuca_launch(moe_glu_dense_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, true, (const float*)gu, dense,
+                ld_dense, (float*)a, n, C, EF, F);
+  else if (dtype == CUCA_BF16)
+    cuca_launch(moe_glu_dense_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, true,
+                (const __nv_bfloat16*)gu, dense, ld_dense, (__nv_bfloat16*)a, n, C, EF, F);
+  else
+    CUCA_REQUIRE(false, "moe_glu_dense: unknown dtype %d", dtype);
+  CUCA_CHECK_LAUNCH("moe_glu_dense");
+  return 0;
+}
+
+CUCA_API int cuca_moe_identity_add(float* y, const void* h, int dtype, const float* ident, int store, int T, int N,
+                                   cudaStream_t stream) {
+  if (T == 0) return 0;
+  const size_t n = (size_t)T * N;
+  size_t blocks = (n + 255) / 256;
+  blocks = blocks > 8192 ? 8192 : blocks;
+  if (dtype == CUCA_F32)
+    cuca_launch(moe_identity_add_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, true, y, (const float*)h,
+                ident, store, n, N);
+  else if (dtype == CUCA_BF16)
+    cuca_launch(moe_identity_add_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, true, y,
+                (const __nv_bfloat16*)h, ident, store, n, N);
+  else
+    CUCA_REQUIRE(false, "moe_identity_add: unknown dtype %d", dtype);
+  CUCA_CHECK_LAUNCH("moe_identity_add");
   return 0;
 }

@@ -102,7 +102,19 @@ _SIGNATURES = {
     "cuca_moe_max_experts": [],
     "cuca_moe_route": [_P, _I, _I, _I, _P, _P, _P, _P],
     "cuca_moe_act_dense": [_P, _P, _P, _I, _I, _I, _I, _P],
-    "cuca_moe_sparse": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "cuca_moe_sparse": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "cuca_moe_route_scored": [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P],
+    "cuca_moe_glu_dense": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
+    "cuca_moe_identity_add": [_P, _P, _I, _P, _I, _I, _I, _P],
+    "cuca_rmsnorm_groups": [_P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P],
+    "cuca_add_partials_rmsnorm_groups": [_P, _P, _I, c_size_t, _P, _P, _I, _P, _I, _I, _F, _I, _P],
+    "cuca_embed_scaled": [_P, _I, _P, _P, _I, _I, _I, _F, _P, _P],
+    "cuca_glu_capped": [_P, _P, _I, _I, _I, _F, _F, _P],
+    "cuca_attention_generic_s": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _F, _I,
+                                 _P, _P],
+    "cuca_norm_rope_store": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I,
+                             _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "cuca_forget_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "cuca_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, c_size_t, _P, _I, _I, _P, _P],
 }
 

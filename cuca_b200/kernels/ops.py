@@ -47,20 +47,23 @@ def _cuda(*tensors):
             raise library.KernelError("kernel arguments must live on the CUDA device (there is no CPU path)")
 
 
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err: torch.Tensor) -> None:
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err: torch.Tensor, scale: float = 1.0) -> None:
+    """out[r] = table[tokens[r]] * scale, into the 32-bit stream."""
     _cuda(table, tokens, out)
     lib = library.load()
     V, E = table.shape
-    library.check(lib.cuca_embed(_p(table), dtype_code(table.dtype), _p(tokens), _p(out), tokens.shape[0], E, V,
-                                 _p(err), _stream()), "embed")
+    library.check(lib.cuca_embed_scaled(_p(table), dtype_code(table.dtype), _p(tokens), _p(out), tokens.shape[0], E, V,
+                                        float(scale), _p(err), _stream()), "embed")
 
 
-def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, rows=None) -> None:
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, rows=None, groups: int = 1) -> None:
+    """out = x / sqrt(mean(x^2) + eps) * weight per row; `groups` > 1: every one of that many equal consecutive parts
+    of a row is divided by its own root mean square."""
     _cuda(x, weight, out)
     lib = library.load()
     n = out.shape[0] if rows is None else rows.shape[0]
-    library.check(lib.cuca_rmsnorm(_p(x), _p(weight), dtype_code(weight.dtype), _p(out), dtype_code(out.dtype),
-                                   _p(rows), n, x.shape[-1], float(eps), _stream()), "rmsnorm")
+    library.check(lib.cuca_rmsnorm_groups(_p(x), _p(weight), dtype_code(weight.dtype), _p(out), dtype_code(out.dtype),
+                                          _p(rows), n, x.shape[-1], float(eps), int(groups), _stream()), "rmsnorm")
 
 
 def rope_store(qkv, positions, seq_of_row, tables, cos, sin, rotary_dim, kpool, vpool, block_size,
@@ -92,6 +95,13 @@ def swiglu(gate_up, out) -> None:
     lib = library.load()
     library.check(lib.cuca_swiglu(_p(gate_up), _p(out), dtype_code(out.dtype), out.shape[0], out.shape[1],
                                   _stream()), "swiglu")
+
+
+def glu_capped(gate_up, out, limit: float, alpha: float) -> None:
+    """out[r, j] = g sigmoid(alpha g) (u + 1), g = min(gate_up[r, j], limit), u = clamp(gate_up[r, ff + j], +-limit)."""
+    _cuda(gate_up, out)
+    library.check(library.load().cuca_glu_capped(_p(gate_up), _p(out), dtype_code(out.dtype), out.shape[0], out.shape[1],
+                                                 float(limit), float(alpha), _stream()), "glu_capped")
 
 
 def add_to_stream(x, delta) -> None:
@@ -591,13 +601,14 @@ def gemm_partial(a, w, err=None, max_slices=16) -> PartialSums:
     return PartialSums(data, slices)
 
 
-def add_partials_rmsnorm(x, partial: PartialSums, weight, out, eps, rows=None) -> None:
+def add_partials_rmsnorm(x, partial: PartialSums, weight, out, eps, rows=None, groups: int = 1) -> None:
     """x += sum of the slices (rows named by `rows`, else all); out = RMSNorm(x) * weight."""
     lib = library.load()
     n = out.shape[0]
-    library.check(lib.cuca_add_partials_rmsnorm(_p(x), _p(partial.data), partial.slices, partial.slice_stride,
-                                                _p(weight), _p(out), dtype_code(out.dtype), _p(rows), n, x.shape[-1],
-                                                float(eps), _stream()), "add_partials_rmsnorm")
+    library.check(lib.cuca_add_partials_rmsnorm_groups(_p(x), _p(partial.data), partial.slices, partial.slice_stride,
+                                                       _p(weight), _p(out), dtype_code(out.dtype), _p(rows), n,
+                                                       x.shape[-1], float(eps), int(groups), _stream()),
+                  "add_partials_rmsnorm")
 
 
 def add_partials(x, partial: PartialSums) -> None:
@@ -805,13 +816,30 @@ def rope_store_general(qkv, k_col, v_col, positions, seq_of_row, tables, cos, si
 
 
 def attention_generic_v(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, n_heads, n_kv_heads,
-                        head_dim, v_head_dim, scale, window, err) -> None:
-    """The plain attention kernel with value heads of their own size (`vpool`: [pages, kv heads, block, v_head_dim])."""
+                        head_dim, v_head_dim, scale, window, err, softcap: float = 0.0, sink: bool = False) -> None:
+    """The plain attention kernel with value heads of their own size (`vpool`: [pages, kv heads, block, v_head_dim]).
+    `softcap` c > 0: a score s becomes c tanh(s / c); `sink`: the softmax's denominator holds one more exp(0)."""
     _cuda(q, out, kpool, vpool)
-    library.check(library.load().cuca_attention_generic_v(
+    library.check(library.load().cuca_attention_generic_s(
         _p(q), int(q_stride), _p(out), out.stride(0), dtype_code(out.dtype), _p(kpool), _p(vpool), kpool.shape[0],
         kpool.shape[2], _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], out.shape[0], n_heads,
-        n_kv_heads, head_dim, v_head_dim, float(scale), int(window or 0), _p(err), _stream()), "attention_generic")
+        n_kv_heads, head_dim, v_head_dim, float(scale), int(window or 0), float(softcap or 0.0), int(bool(sink)),
+        _p(err), _stream()), "attention_generic")
+
+
+def norm_rope_store(qkv, k_col, v_col, positions, seq_of_row, tables, cos, sin, rotary_dim, adjacent, q_norm, k_norm,
+                    v_norm: bool, eps: float, kpool, vpool, block_size, n_heads, n_kv_heads, head_dim, v_head_dim, err,
+                    v_split: int = 1, q_out=None) -> None:
+    """`rope_store_general` with norms per head in 32-bit before the rotation: q / rms(q) * q_norm, k likewise with
+    k_norm (None: no norm), and with `v_norm` v / rms(v) before it is kept. q is rewritten in place, or goes to
+    `q_out` [rows, heads * head_dim] of the pools' dtype (32-bit rows beside 16-bit pools)."""
+    _cuda(qkv, positions, seq_of_row, kpool, vpool, q_norm, k_norm, q_out)
+    library.check(library.load().cuca_norm_rope_store(
+        _p(qkv), dtype_code(qkv.dtype), qkv.stride(0), int(k_col), int(v_col), _p(q_out), dtype_code(kpool.dtype),
+        _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(cos), _p(sin),
+        cos.shape[0] if cos is not None else 0, int(rotary_dim), int(bool(adjacent)), _p(q_norm), _p(k_norm),
+        int(bool(v_norm)), float(eps), _p(kpool), _p(vpool), kpool.shape[0], int(block_size), qkv.shape[0], n_heads,
+        n_kv_heads, head_dim, v_head_dim, int(v_split), _p(err), _stream()), "norm_rope_store")
 
 
 def sigmoid_gate_(a, gate) -> None:
@@ -894,6 +922,18 @@ def mlstm_scan(proj, q_col, k_col, v_col, i_col, f_col, i_bias, f_bias, cap, mem
     library.launches += 2  # the gates are prepared by a launch of their own, the new n and m moved in by another
 
 
+def forget_scan(proj, q_col, f_col, v_col, f_bias, lower, state, out, step, H, d, dv) -> None:
+    """Linear attention whose forget gate is also one minus its write strength, along every request's rows (see
+    `parts/recurrent.py:ForgetGateAttention`). The q and gate columns of `proj` hold pre-activations and are rewritten
+    in place (silu; the gate above its lower bound) before the scan; two launches."""
+    _cuda(proj, f_bias, lower, state, out)
+    library.check(library.load().cuca_forget_scan(
+        _p(proj), proj.stride(0), int(q_col), int(f_col), int(v_col), _p(f_bias), _p(lower), _p(state), _p(out),
+        _p(step.seq_of_row), _p(step.req_row0), _p(step.req_count), _p(step.slots), proj.shape[0], step.n_seqs, H, d, dv,
+        _stream()), "forget_scan")
+    library.launches += 1
+
+
 def head_norm_gate(o, weight, per_head: bool, gate, out, H, dv, eps) -> None:
     """out[r, h] = o[r, h] / rms(o[r, h]) * weight * sigmoid(gate[r, h]); weight [dv] for every head or [H dv]."""
     _cuda(o, weight, gate, out)
@@ -919,9 +959,38 @@ def moe_act_dense(u, dense, a, E, F) -> None:
                                                     _stream()), "moe_act_dense")
 
 
-def moe_sparse(h, w_up, w_down, idx, wts, a, y, store, top, E, F) -> None:
-    """y (+)= sum over a token's chosen experts of weight * down_e(relu(up_e h)^2), reading only those experts."""
+def moe_sparse(h, w_up, w_down, idx, wts, a, y, store, top, E, F, glu: bool = False) -> None:
+    """y (+)= sum over a token's chosen experts of weight * down_e(act_e h), reading only those experts. Plain:
+    act = relu(up h)^2, `w_up` [E F, K], `w_down` [N, E F]. `glu`: act = silu(gate h) * (up h), `w_up` [2 C, K] (all
+    gates, then all ups), `w_down` [N, C], C >= E F. Pairs that name expert E or more (experts without weights) are
+    skipped."""
     _cuda(h, w_up, w_down, idx, wts, a, y)
     library.check(library.load().cuca_moe_sparse(_p(h), _p(w_up), _p(w_down), _p(idx), _p(wts), _p(a), _p(y),
                                                  int(bool(store)), dtype_code(h.dtype), h.shape[0], int(top), E, F,
-                                                 h.shape[1], y.shape[1], _stream()), "moe_sparse")
+                                                 h.shape[1], y.shape[1], int(bool(glu)), w_down.shape[1], _stream()),
+                  "moe_sparse")
+    library.launches += 1
+
+
+def moe_route_scored(logits, correction, n_real, top, idx, wts, dense=None, ident=None) -> None:
+    """Scores s = softmax over all router outputs; the `top` largest of s + correction are chosen (`correction` None:
+    of s); weights s / (sum of the chosen s + 1e-20). Outputs from `n_real` on are experts that return their input:
+    `ident[t]` gets the sum of their chosen weights."""
+    _cuda(logits, correction, idx, wts, dense, ident)
+    library.check(library.load().cuca_moe_route_scored(_p(logits), _p(correction), logits.shape[0], logits.shape[1],
+                                                       int(n_real), int(top), _p(idx), _p(wts), _p(dense), _p(ident),
+                                                       _stream()), "moe_route_scored")
+
+
+def moe_glu_dense(gu, dense, a, EF, F) -> None:
+    """a[t, c] = silu(gu[t, c]) * gu[t, C + c] * w, w = dense[t, c // F] for c < EF and 1 behind (a shared expert)."""
+    _cuda(gu, dense, a)
+    library.check(library.load().cuca_moe_glu_dense(_p(gu), _p(dense), dense.shape[1], _p(a), dtype_code(gu.dtype),
+                                                    gu.shape[0], a.shape[1], int(EF), int(F), _stream()), "moe_glu_dense")
+
+
+def moe_identity_add(y, h, ident, store: bool) -> None:
+    """y[t] (+)= ident[t] * h[t]."""
+    _cuda(y, h, ident)
+    library.check(library.load().cuca_moe_identity_add(_p(y), _p(h), dtype_code(h.dtype), _p(ident), int(bool(store)),
+                                                       h.shape[0], h.shape[1], _stream()), "moe_identity_add")

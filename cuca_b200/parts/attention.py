@@ -15,6 +15,11 @@ Values may have a size of their own (`v_head_dim`), the concatenated heads may p
 sigmoid(W_g h) before the output projection (`gate`), and the rotation may pair adjacent dimensions: any of these
 takes the general path (one stacked projection q | k | v | gate, a rotate-and-store kernel that knows the columns,
 the plain attention kernel with value rows of their own size).
+
+Further options of the general path: an RMS norm per head on queries and keys with a weight of the head's size shared
+by the heads (`qk_norm`, before the rotation) and on values without a weight (`v_norm`, before they are kept), a
+smooth cap on the scaled score, c tanh(s / c) (`softcap`), and a sink: one more term exp(0), with no value, in the
+softmax's denominator (`sink`).
 """
 from __future__ import annotations
 
@@ -30,8 +35,9 @@ from .base import POSITIONS, CacheNeeds, KvNeeds, Mixer, PartSpec, TensorNeed, r
 @register_mixer("attention")
 class PagedAttention(Mixer):
     """params: width, n_heads, n_kv_heads, head_dim, window (None: all keys), scale (None: 1/sqrt(head_dim)),
-    position (PartSpec or None), shares_cache (bool), v_head_dim (None: head_dim), gate (bool). tensors: q, k, v, o,
-    g (with `gate`) and optional q_bias, k_bias, v_bias, o_bias."""
+    position (PartSpec or None), shares_cache (bool), v_head_dim (None: head_dim), gate (bool), qk_norm (bool),
+    v_norm (bool), eps (of those norms), softcap (None or 0: none), sink (bool). tensors: q, k, v, o, g (with `gate`),
+    q_norm and k_norm [head_dim] (with `qk_norm`) and optional q_bias, k_bias, v_bias, o_bias."""
 
     graph_safe = True
 
@@ -47,6 +53,12 @@ class PagedAttention(Mixer):
         self.shares_cache = bool(p.get("shares_cache", False))
         self.v_head_dim = int(p["v_head_dim"]) if p.get("v_head_dim") else self.head_dim
         self.gated = bool(p.get("gate", False))
+        self.qk_norm, self.v_norm = bool(p.get("qk_norm", False)), bool(p.get("v_norm", False))
+        self.eps = float(p.get("eps", 1e-6))
+        self.softcap = float(p.get("softcap") or 0.0)
+        self.sink = bool(p.get("sink", False))
+        if self.softcap < 0:
+            raise ValueError(f"attention: a score cap of {self.softcap} is not positive")
         if self.n_heads % self.n_kv_heads:
             raise ValueError(f"{self.n_kv_heads} key heads must divide {self.n_heads} query heads")
         if not 1 <= self.head_dim <= ops.ATTENTION_MAX_HEAD_DIM:
@@ -54,13 +66,14 @@ class PagedAttention(Mixer):
                              f"(1..{ops.ATTENTION_MAX_HEAD_DIM})")
         pos = p.get("position")
         self.position = POSITIONS.get(pos.kind)(pos, runtime) if isinstance(pos, PartSpec) else None
-        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.w_qn = self.w_kn = None
         # what the stacked-projection kernels of the usual path do not take
-        self.general = (self.v_head_dim != self.head_dim or self.gated
+        self.normed = self.qk_norm or self.v_norm
+        self.general = (self.v_head_dim != self.head_dim or self.gated or self.normed or self.softcap > 0 or self.sink
                         or getattr(self.position, "pairs", "half") != "half")
         if self.general and self.shares_cache:
             raise ValueError("attention: a layer that reads another layer's pages takes neither a value size of its "
-                             "own, an output gate nor adjacent rotation pairs")
+                             "own, an output gate, head norms, a score cap, a sink nor adjacent rotation pairs")
         if self.general and not 1 <= self.v_head_dim <= 2 * ops.ATTENTION_MAX_HEAD_DIM:
             raise ValueError(f"attention: value size {self.v_head_dim} is outside what the kernels take "
                              f"(1..{2 * ops.ATTENTION_MAX_HEAD_DIM})")
@@ -76,6 +89,9 @@ class PagedAttention(Mixer):
                t["o"]: TensorNeed((self.width, self.n_heads * dv))}
         if self.gated:
             out[t["g"]] = TensorNeed((self.n_heads * dv, self.width))
+        if self.qk_norm:
+            out[t["q_norm"]] = TensorNeed((d,), keep_fp32=True, init="ones")
+            out[t["k_norm"]] = TensorNeed((d,), keep_fp32=True, init="ones")
         if not self.shares_cache:
             out[t["k"]] = TensorNeed((self.n_kv_heads * d, self.width))
             out[t["v"]] = TensorNeed((self.n_kv_heads * dv, self.width))
@@ -97,9 +113,11 @@ class PagedAttention(Mixer):
             self.b_qkv = torch.cat(biases).contiguous()
         self.w_o = get(t["o"])
         self.b_o = get(t["o_bias"]) if "o_bias" in t else None
+        if self.qk_norm:
+            self.w_qn, self.w_kn = get(t["q_norm"]), get(t["k_norm"])
 
     def weight_bytes(self):
-        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o, self.b_qkv, self.b_o)
+        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o, self.b_qkv, self.b_o, self.w_qn, self.w_kn)
                    if w is not None)
 
     def prepare(self, context_length: int) -> None:
@@ -118,6 +136,8 @@ class PagedAttention(Mixer):
         once per slab against the same keys. 0: value rows as they are, for the plain kernel. The answer depends on
         the layer's sizes, the compute dtype and the page size alone, so every step lays the pool out alike."""
         d, dv, bs = self.head_dim, self.v_head_dim, cache.block_size
+        if self.softcap > 0 or self.sink:  # the tensor-core kernels know neither
+            return 0
         if (self.rt.dtype == torch.bfloat16 and dv % d == 0 and bs & (bs - 1) == 0
                 and ops.attention_mma_supported(self.n_heads, self.n_kv_heads, d, self.w_qkv.shape[0], self.n_heads * d)):
             return dv // d
@@ -138,9 +158,14 @@ class PagedAttention(Mixer):
                              "the step's per-request description")
         tensor_cores = split >= 1 and plan is not None
         split = max(split, 1)
-        ops.rope_store_general(proj, nh * d, (nh + nkv) * d, step.positions, step.seq_of_row, cache.tables, cos, sin,
-                               rot, adjacent, cache.k, cache.v, cache.block_size, nh, nkv, d, dv, self.rt.err,
-                               v_split=split)
+        if self.normed:
+            ops.norm_rope_store(proj, nh * d, (nh + nkv) * d, step.positions, step.seq_of_row, cache.tables, cos, sin,
+                                rot, adjacent, self.w_qn, self.w_kn, self.v_norm, self.eps, cache.k, cache.v,
+                                cache.block_size, nh, nkv, d, dv, self.rt.err, v_split=split)
+        else:
+            ops.rope_store_general(proj, nh * d, (nh + nkv) * d, step.positions, step.seq_of_row, cache.tables, cos, sin,
+                                   rot, adjacent, cache.k, cache.v, cache.block_size, nh, nkv, d, dv, self.rt.err,
+                                   v_split=split)
         gate = proj[:, (nh + nkv) * d + nkv * dv:] if self.gated else None
         attn = self.rt.empty(rows, nh * dv)
         if tensor_cores:
@@ -153,7 +178,8 @@ class PagedAttention(Mixer):
                 ops.gate_merge(parts, gate, attn, nh, dv)
         else:
             ops.attention_generic_v(proj, proj.stride(0), attn, cache.k, cache.v, step.positions, step.seq_of_row,
-                                    cache.tables, nh, nkv, d, dv, self.scale, self.window, self.rt.err)
+                                    cache.tables, nh, nkv, d, dv, self.scale, self.window, self.rt.err,
+                                    softcap=self.softcap, sink=self.sink)
             if gate is not None:
                 ops.sigmoid_gate_(attn, gate)
         stream.add_linear(attn, self.w_o, bias=self.b_o)

@@ -2,7 +2,8 @@
 (src/provider/local/model/cpu.rs:2650-2704 with pre_norms on, post_norms off).
 `sandwich_shift`: a norm before and after each sublayer, and the mixer reads its input mixed with the previous
 token's: x += n1b(mixer(shift(n1(x)))); x += n2b(ffn(n2(x))).
-`hyper_connections`: several copies of the stream; a sublayer reads a weighted sum of them and writes into all."""
+`hyper_connections`: several copies of the stream; a sublayer reads a weighted sum of them and writes into all.
+`parallel_residual`: one norm, both sublayers read its output: x += mixer(h) + ffn(h) with h = norm(x)."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -18,6 +19,18 @@ class PreNormBlock(Block):
         if self.feed_forward is not None:
             f = self.ffn_norm.forward(stream)
             self.feed_forward.forward(f, stream, step)
+
+
+@register_block("parallel_residual")
+class ParallelResidualBlock(Block):
+    """x += mixer(h) + ffn(h) with the one h = norm(x): the layer's `mixer_norm` is its only norm (an `ffn_norm` is
+    not used). Both sublayers add into the stream; neither reads it, so their order does not matter."""
+
+    def forward(self, stream, step, cache) -> None:
+        h = self.mixer_norm.forward(stream)
+        self.mixer.forward(h, stream, step, cache)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(h, stream, step)
 
 
 @register_block("sandwich_shift")

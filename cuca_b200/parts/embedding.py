@@ -13,12 +13,13 @@ from .base import Part, TensorNeed
 
 
 class TokenEmbedding(Part):
-    """params: vocab, width. tensors: weight [vocab, width]."""
+    """params: vocab, width, scale (a factor on every embedding row, default 1). tensors: weight [vocab, width]."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.vocab = int(spec.params["vocab"])
         self.width = int(spec.params["width"])
+        self.scale = float(spec.params.get("scale", 1.0))
         self.weight = None
 
     def tensors(self):
@@ -28,7 +29,7 @@ class TokenEmbedding(Part):
         self.weight = get(self.spec.tensors["weight"])
 
     def forward(self, tokens, out) -> None:
-        ops.embed(self.weight, tokens, out, self.rt.err)
+        ops.embed(self.weight, tokens, out, self.rt.err, self.scale)
 
 
 class OutputHead(Part):

@@ -8,12 +8,16 @@ from .base import Norm, TensorNeed, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    """params: width, eps. tensors: weight [width]."""
+    """params: width, eps, groups (default 1: the whole row; g: the row is cut into g equal consecutive parts and each
+    is divided by its own root mean square before the weight multiplies the whole). tensors: weight [width]."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.width = int(spec.params["width"])
         self.eps = float(spec.params["eps"])
+        self.groups = int(spec.params.get("groups") or 1)
+        if self.groups < 1 or self.width % self.groups:
+            raise ValueError(f"rmsnorm: {self.groups} parts do not divide the width {self.width}")
         self.weight = self.gain = None
 
     def tensors(self):
@@ -32,9 +36,9 @@ class RMSNorm(Norm):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = self.rt.empty(n, self.width)
         if pending is not None:
-            ops.add_partials_rmsnorm(x, pending, self.weight, out, self.eps, rows)
+            ops.add_partials_rmsnorm(x, pending, self.weight, out, self.eps, rows, groups=self.groups)
         else:
-            ops.rmsnorm(x, self.weight, out, self.eps, rows)
+            ops.rmsnorm(x, self.weight, out, self.eps, rows, groups=self.groups)
         return out
 
 

@@ -272,3 +272,54 @@ class MatrixLSTM(Mixer):
         out = rt.empty(rows, H * dv)
         ops.head_norm_gate(o, self.norm_w, True, proj[:, g_col:i_col], out, H, dv, self.eps)
         rt.stream(stream).add_linear(out, self.w_o)
+
+
+@register_mixer("hgrn2")
+class ForgetGateAttention(Mixer):
+    """HGRN2: linear attention whose forget gate also decides what is written. q = silu(W_q h) (heads x dim),
+    v = W_v h (heads x vdim), f = l + (1 - l) sigmoid(W_f h + b_f) per head and key channel with a lower bound l in
+    [0, 1] per channel (a stored vector); per head, S of dim x vdim (zero at the start):
+        S <- f[:, None] * S + (1 - f)[:, None] * v[None, :];   o = S^T q     (there is no key and no scale);
+    o / rms(o) per head, times `norm` [vdim] (shared by the heads), then W_o. State: S in 32-bit.
+    params: width, heads, dim, vdim, eps. tensors: q, f, f_bias, lower, v, norm, o."""
+
+    graph_safe = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.width, self.heads = int(p["width"]), int(p["heads"])
+        self.dim, self.vdim, self.eps = int(p["dim"]), int(p["vdim"]), float(p["eps"])
+        if self.dim > ops.MATRIX_STATE_MAX_DIM:
+            raise ValueError(f"hgrn2: {self.dim} key channels exceed {ops.MATRIX_STATE_MAX_DIM}")
+        self.w_in = self.f_bias = self.lower = self.norm_w = self.w_o = None
+
+    def cache_needs(self):
+        return CacheNeeds(state={"memory": StateNeeds((self.heads, self.vdim, self.dim))})
+
+    def tensors(self):
+        t, E, H = self.spec.tensors, self.width, self.heads
+        return {t["q"]: TensorNeed((H * self.dim, E)), t["f"]: TensorNeed((H * self.dim, E)),
+                t["f_bias"]: TensorNeed((H * self.dim,), keep_fp32=True),
+                t["lower"]: TensorNeed((H * self.dim,), keep_fp32=True),
+                t["v"]: TensorNeed((H * self.vdim, E)),
+                t["norm"]: TensorNeed((self.vdim,), keep_fp32=True, init="ones"), t["o"]: TensorNeed((E, H * self.vdim))}
+
+    def load(self, get):
+        t = self.spec.tensors
+        self.w_in = torch.cat([get(t[r]) for r in ("q", "f", "v")], dim=0).contiguous()
+        self.f_bias, self.lower = get(t["f_bias"]), get(t["lower"])
+        self.norm_w, self.w_o = get(t["norm"]), get(t["o"])
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.f_bias, self.lower, self.norm_w, self.w_o))
+
+    def forward(self, h, stream, step, cache) -> None:
+        rt, rows = self.rt, h.shape[0]
+        H, d, dv = self.heads, self.dim, self.vdim
+        proj = rt.linear(h, self.w_in, out_dtype=torch.float32)  # [q | f | v]
+        o = rt.empty(rows, H * dv, dtype=torch.float32)
+        ops.forget_scan(proj, 0, H * d, 2 * H * d, self.f_bias, self.lower, cache.state["memory"], o, step, H, d, dv)
+        out = rt.empty(rows, H * dv)
+        ops.head_norm_gate(o, self.norm_w, False, None, out, H, dv, self.eps)
+        rt.stream(stream).add_linear(out, self.w_o)
