@@ -228,6 +228,27 @@ def _dupenex_config(width, ff, heads, layers, vocab, window):
             "loop": {"start": 0, "stop": layers // 2, "times": 2}}
 
 
+def _pudinex_config(width, ff, heads, layers, vocab, window):
+    """`layers` layers, every third one softmax attention (heads of 128, a quarter as many key heads, values as wide as
+    keys, half of a head rotated with YaRN-scaled frequencies, head norms, a score cap and a sink), the others HGRN2
+    (heads of 128 x 128); the first layer's feed-forward is the dense capped unit, the others are routed (eight experts
+    of ff / 4 and two that return their input, two chosen, and a shared expert of ff / 4). One norm per layer in two
+    parts. `window` is unused: the design has none."""
+    H = max(1, width // 128)
+    attention = {"type": "attention",
+                 "mixer": {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                           "softcap": 30.0,
+                           "rot": {"base": 10000.0, "dims": 64,
+                                   "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    forget = {"type": "hgrn2", "mixer": {"heads": H, "dim": 128, "vdim": 128}}
+    routed = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 8, "identity": 2, "top": 2},
+              "shared": {"ff": ff // 4}}
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    return {"architecture": "Pudinex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 2},
+            "embedding": {"scale": 1.0},
+            "layers": [dict(attention if i % 3 == 2 else forget, mlp=dense if i == 0 else routed) for i in range(layers)]}
+
+
 def _llama_config(width, ff, heads, layers, vocab):
     return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers,
             "hidden_size": width, "num_attention_heads": heads, "num_key_value_heads": max(1, heads // 4),
@@ -257,8 +278,8 @@ def design_table(args) -> int:
     ctx = max(T, P + steps + warmup + 64) + 64
     for size in (args.sizes.split(",") if args.sizes else list(DESIGN_SIZES)):
         width, ff, heads, layers, vocab = DESIGN_SIZES[size]
-        runs = layers + layers // 2  # the looped half runs twice
-        make = {"bananex": _bananex_config, "dupenex": _dupenex_config}[args.design]
+        runs = layers if args.design == "pudinex" else layers + layers // 2  # (a looped half runs twice)
+        make = {"bananex": _bananex_config, "dupenex": _dupenex_config, "pudinex": _pudinex_config}[args.design]
         for name, cfg in ((args.design, make(width, ff, heads, layers, vocab, window=1024)),
                           ("llama", _llama_config(width, ff, heads, runs, vocab))):
             if args.only_model and name != args.only_model:
@@ -347,7 +368,7 @@ def main() -> int:
     ap.add_argument("--decode-only", action="store_true",
                     help="with --shape llama-3.2-1b: the plain decode line at --batch instead of the mixed workload")
     ap.add_argument("--only-model", default=None, help="with --design: run only this model of the pair (the design's name or llama)")
-    ap.add_argument("--design", default=None, choices=["bananex", "dupenex"],
+    ap.add_argument("--design", default=None, choices=["bananex", "dupenex", "pudinex"],
                     help="instead of the bench: prefill and decode of this design beside a Llama of equal width, "
                          "feed-forward size and layer runs, at --sizes (1b,3b,8b layer sizes; a few layers each)")
     ap.add_argument("--sizes", default=None, help="with --design: which of 1b,3b,8b (all else)")

@@ -60,6 +60,9 @@ struct Params {
   int n_tiles;           // tiles of the launch (heaviest first)
   int pair_tiles;        // 1: CTA b takes tile b and then tile n_tiles - 1 - b (a heavy and a light one)
   float scale_log2e;
+  float cap_log2e;       // > 0: a score s becomes cap tanh(s / cap); this is cap log2(e), and ...
+  float cap_arg;         // ... 2 scale log2(e) / cap: exp2(raw cap_arg) = e^(2 s / cap)
+  int sink;              // 1: the denominator holds one more exp(0)
   int window;
   int* err;
 };
@@ -125,6 +128,12 @@ __device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: exp2(-inf)
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// cap tanh(s / cap) in log2 units from the raw score: tanh(y) = 1 - 2 / (e^(2 y) + 1), exact at both ends
+// (e^(2 y) = inf gives 1, 0 gives -1); `arg` = 2 scale log2(e) / cap, `cap_l2` = cap log2(e)
+__device__ __forceinline__ float capped_log2(float raw, float arg, float cap_l2) {
+  const float e = fast_exp2(raw * arg);
+  return cap_l2 - __fdividef(2.f * cap_l2, e + 1.f);
 }
 // as tmem_ld32 without the wait: several loads can be in flight before one tmem_ld_wait()
 __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
@@ -409,7 +418,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
         }
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2e;
+      const bool capped = p.cap_log2e > 0.f;
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // (the cap grows with the score, so the largest raw score is the largest capped one)
+      mx = capped ? (mx == -INFINITY ? mx : capped_log2(mx, p.cap_arg, p.cap_log2e)) : mx * p.scale_log2e;
       // The running maximum only moves when the new one exceeds it by more than 8 (in log2 units): values up to
       // 2^8 above the reference are exact enough in 32-bit sums, and O is rescaled far less often.
       float m_new = m;
@@ -423,6 +435,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       uint32_t pw[KEYS / 2];
       const float2 scale2 = make_float2(p.scale_log2e, p.scale_log2e), neg_m2 = make_float2(-m_use, -m_use);
+      if (capped) {
+        // two more exponent-unit operations per score (the tanh); a masked score stays masked
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float r0 = __uint_as_float(raw[c][2 * e]), r1 = __uint_as_float(raw[c][2 * e + 1]);
+            const float x0 = r0 == -INFINITY ? r0 : capped_log2(r0, p.cap_arg, p.cap_log2e) - m_use;
+            const float x1 = r1 == -INFINITY ? r1 : capped_log2(r1, p.cap_arg, p.cap_log2e) - m_use;
+            const float2 p2 = make_float2(fast_exp2(x0), fast_exp2(x1));
+            sum2[e & 1] = __fadd2_rn(sum2[e & 1], p2);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(p2.x, p2.y);
+            pw[c * 16 + e] = *reinterpret_cast<uint32_t*>(&t2);
+          }
+        }
+      } else {
 #pragma unroll
       for (int c = 0; c < NC; ++c) {
 #pragma unroll
@@ -433,6 +461,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           __nv_bfloat162 t2 = __floats2bfloat162_rn(p2.x, p2.y);
           pw[c * 16 + e] = *reinterpret_cast<uint32_t*>(&t2);
         }
+      }
       }
       static_assert(KEYS == 64, "one 32-column store holds the P row of a 64-key tile");
       tmem_st32_raw(tmem_s(x, j) + lane_bits, pw);
@@ -460,6 +489,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     if (ok && __all_sync(0xffffffffu, mbar_wait(&pv_done[x], (n_tiles - 1) & 1, p.err, abort_flag))) {
       tc_fence_after();
+      if (p.sink) l += (m == -INFINITY) ? 1.f : fast_exp2(-m);  // the sink's score is 0; m is the reference in log2 units
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* dst = p.out + (size_t)(row0 + r) * p.out_stride + (size_t)(head0 + x) * D;
 #pragma unroll
@@ -536,8 +566,8 @@ CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_t
                                        const void* kpool, const void* vpool, int n_blocks, int bs,
                                        const int* positions, const int* seq_of_row, const int* tables,
                                        int table_stride, const int* tile_row0, const int* tile_nrows, int n_tiles,
-                                       int nh, int nkv, int d, float scale, int window, int* err,
-                                       cudaStream_t stream) {
+                                       int nh, int nkv, int d, float scale, int window, float softcap, int sink,
+                                       int* err, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   CUCA_REQUIRE(cuca_attention_tc_supported(nh, nkv, d, bs, q_stride, out_stride, q, kpool, vpool),
                "attention_prefill_tc: unsupported shape (heads %d/%d, head size %d, page %d)", nh, nkv, d, bs);
@@ -552,6 +582,9 @@ CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_t
   p.positions = positions; p.seq_of_row = seq_of_row; p.tile_row0 = tile_row0; p.tile_nrows = tile_nrows;
   p.n_blocks = n_blocks; p.bs = bs; p.nh = nh; p.nkv = nkv; p.scale_log2e = scale * 1.4426950408889634f;
   p.window = window; p.err = err;
+  p.cap_log2e = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  p.cap_arg = softcap > 0.f ? 2.f * scale * 1.4426950408889634f / softcap : 0.f;
+  p.sink = sink ? 1 : 0;
   p.heads_per_cta = ((nh / nkv) % NQ == 0) ? NQ : 1;
   p.n_tiles = n_tiles;
   // Two tiles per CTA, a heavy and a light one, where that makes one round of CTAs out of more than one

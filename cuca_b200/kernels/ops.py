@@ -382,13 +382,17 @@ def _decode_scratch(device, n_rows, n_heads, n_kv_heads, head_dim, n_splits):
 
 
 def attention_decode(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, rows, n_rows, n_heads,
-                     n_kv_heads, head_dim, scale, window, chunk, n_splits, err) -> None:
+                     n_kv_heads, head_dim, scale, window, chunk, n_splits, err, softcap: float = 0.0,
+                     sink: bool = False) -> None:
+    """The split-key decode form. `softcap` c > 0: a scaled score s becomes c tanh(s / c); `sink`: every row's
+    denominator holds one more exp(0) that has no value."""
     lib = library.load()
     part, cnt = _decode_scratch(out.device, n_rows, n_heads, n_kv_heads, head_dim, n_splits)
-    library.check(lib.cuca_attention_decode(
+    library.check(lib.cuca_attention_decode_s(
         _p(q), int(q_stride), _p(out), out.stride(0), _p(kpool), _p(vpool), kpool.shape[0], kpool.shape[2],
         _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(rows), n_rows, n_heads, n_kv_heads, head_dim,
-        float(scale), int(window or 0), chunk, n_splits, _p(part), _p(cnt), _p(err), _stream()), "attention_decode")
+        float(scale), int(window or 0), float(softcap or 0.0), int(bool(sink)), chunk, n_splits, _p(part), _p(cnt),
+        _p(err), _stream()), "attention_decode")
 
 
 def attention_decode_fused(partial, bias, cos, sin, rotary_dim, has_kv, out, kpool, vpool, positions, seq_of_row, tables,
@@ -415,12 +419,13 @@ def attention_decode_fused_supported(plan, cache, out_dtype, n_rows, n_heads, n_
 
 
 def attention_prefill(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, tile_row0, tile_nrows, n_tiles,
-                      n_heads, n_kv_heads, head_dim, scale, window, err) -> None:
+                      n_heads, n_kv_heads, head_dim, scale, window, err, softcap: float = 0.0, sink: bool = False) -> None:
     lib = library.load()
-    library.check(lib.cuca_attention_prefill(
+    library.check(lib.cuca_attention_prefill_s(
         _p(q), int(q_stride), _p(out), out.stride(0), _p(kpool), _p(vpool), kpool.shape[0], kpool.shape[2],
         _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(tile_row0), _p(tile_nrows), n_tiles, n_heads,
-        n_kv_heads, head_dim, float(scale), int(window or 0), _p(err), _stream()), "attention_prefill")
+        n_kv_heads, head_dim, float(scale), int(window or 0), float(softcap or 0.0), int(bool(sink)), _p(err),
+        _stream()), "attention_prefill")
 
 
 def attention_tc_supported(q, out, kpool, vpool, n_heads, n_kv_heads, head_dim) -> bool:
@@ -442,20 +447,24 @@ def attention_pair_tiles_mode(mode: int) -> None:
 
 
 def attention_prefill_tc(q, out, kpool, vpool, positions, seq_of_row, tables, tile_row0, tile_nrows, n_tiles,
-                         n_heads, n_kv_heads, head_dim, scale, window, err) -> None:
+                         n_heads, n_kv_heads, head_dim, scale, window, err, softcap: float = 0.0,
+                         sink: bool = False) -> None:
     """Prefill attention on tcgen05; tiles of up to 128 consecutive rows of one request."""
     lib = library.load()
     library.check(lib.cuca_attention_prefill_tc(
         _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(kpool), _p(vpool), kpool.shape[0], kpool.shape[2],
         _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(tile_row0), _p(tile_nrows), n_tiles, n_heads,
-        n_kv_heads, head_dim, float(scale), int(window or 0), _p(err), _stream()), "attention_prefill_tc")
+        n_kv_heads, head_dim, float(scale), int(window or 0), float(softcap or 0.0), int(bool(sink)), _p(err),
+        _stream()), "attention_prefill_tc")
 
 
-def attention(qkv, out, cache, step, plan, n_heads, n_kv_heads, head_dim, scale, window, err) -> None:
+def attention(qkv, out, cache, step, plan, n_heads, n_kv_heads, head_dim, scale, window, err, softcap: float = 0.0,
+              sink: bool = False) -> None:
     """Paged causal attention of every row of the step; q is the head of each `qkv` row. bfloat16 with head
     sizes 16..128 in steps of 16 runs on tensor cores: single-token requests through the split-key decode form,
     portions of prompts through the prefill form; everything else (the 32-bit path, other head sizes) through
-    the plain kernel."""
+    the plain kernel. `softcap` c > 0: a scaled score s becomes c tanh(s / c); `sink`: one more exp(0) without a
+    value in every row's denominator."""
     bs = cache.block_size
     if (out.dtype == torch.bfloat16 and plan is not None and bs & (bs - 1) == 0
             and attention_mma_supported(n_heads, n_kv_heads, head_dim, qkv.stride(0), out.stride(0))):
@@ -463,19 +472,20 @@ def attention(qkv, out, cache, step, plan, n_heads, n_kv_heads, head_dim, scale,
             if USE_TC_ATTENTION and attention_tc_supported(qkv, out, cache.k, cache.v, n_heads, n_kv_heads, head_dim):
                 row0, nrows, n = plan.tiles(tile_rows(1))
                 attention_prefill_tc(qkv, out, cache.k, cache.v, step.positions, step.seq_of_row, cache.tables,
-                                     row0, nrows, n, n_heads, n_kv_heads, head_dim, scale, window, err)
+                                     row0, nrows, n, n_heads, n_kv_heads, head_dim, scale, window, err, softcap, sink)
             else:
                 row0, nrows, n = plan.tiles(tile_rows(0))
                 attention_prefill(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
-                                  cache.tables, row0, nrows, n, n_heads, n_kv_heads, head_dim, scale, window, err)
+                                  cache.tables, row0, nrows, n, n_heads, n_kv_heads, head_dim, scale, window, err,
+                                  softcap, sink)
         if plan.n_decode:
             chunk, n_splits = plan.chunk(n_kv_heads, head_dim)
             attention_decode(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
                              cache.tables, plan.decode_rows, plan.n_decode, n_heads, n_kv_heads, head_dim, scale,
-                             window, chunk, n_splits, err)
+                             window, chunk, n_splits, err, softcap, sink)
         return
-    attention_generic(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row, cache.tables,
-                      n_heads, n_kv_heads, head_dim, scale, window, err)
+    attention_generic_v(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row, cache.tables,
+                        n_heads, n_kv_heads, head_dim, head_dim, scale, window, err, softcap=softcap, sink=sink)
 
 
 def scatter_int(dst, idx, val) -> None:

@@ -136,8 +136,6 @@ class PagedAttention(Mixer):
         once per slab against the same keys. 0: value rows as they are, for the plain kernel. The answer depends on
         the layer's sizes, the compute dtype and the page size alone, so every step lays the pool out alike."""
         d, dv, bs = self.head_dim, self.v_head_dim, cache.block_size
-        if self.softcap > 0 or self.sink:  # the tensor-core kernels know neither
-            return 0
         if (self.rt.dtype == torch.bfloat16 and dv % d == 0 and bs & (bs - 1) == 0
                 and ops.attention_mma_supported(self.n_heads, self.n_kv_heads, d, self.w_qkv.shape[0], self.n_heads * d)):
             return dv // d
@@ -173,7 +171,7 @@ class PagedAttention(Mixer):
             parts = self.rt.empty(split, rows, nh * d) if (split > 1 or gate is not None) else attn.view(1, rows, nh * d)
             for j in range(split):
                 ops.attention(proj, parts[j], dataclasses.replace(cache, v=slabs[j]), step, plan, nh, nkv, d, self.scale,
-                              self.window, self.rt.err)
+                              self.window, self.rt.err, softcap=self.softcap, sink=self.sink)
             if parts.data_ptr() != attn.data_ptr():
                 ops.gate_merge(parts, gate, attn, nh, dv)
         else:
