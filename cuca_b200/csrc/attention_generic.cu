@@ -161,7 +161,9 @@ CUCA_API int cuca_attention_generic(const void* q, int q_stride, void* out, int 
 // v_col. The first `rot` values of every q and k head are rotated by the row's position, in pairs (i, i + rot/2)
 // (pairs 0) or (2i, 2i + 1) (pairs 1); q in place, k and v go to the position's page. v_split r > 1: the value pool
 // is r slabs [n_blocks][nkv][bs][dv / r], slab j holding values j dv/r .. (j+1) dv/r - 1 of every head (each slab is
-// then a value pool of narrower heads for the kernels that want values as wide as keys).
+// then a value pool of narrower heads for the kernels that want values as wide as keys). dv_src < dv: a row's value
+// heads hold dv_src values and the pool's dv: the rest of a pool row is written as zeros (values padded to a
+// multiple of the key size for those kernels).
 namespace {
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -169,7 +171,7 @@ rope_store_general_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, con
                           const int* __restrict__ seq_of_row, const int* __restrict__ tables, int table_stride,
                           const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_rows, int rot,
                           int pairs, T* __restrict__ kpool, T* __restrict__ vpool, int n_blocks, int bs, int nh,
-                          int nkv, int d, int dv, int v_split, int* err) {
+                          int nkv, int d, int dv, int v_split, int dv_src, int* err) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
@@ -218,7 +220,8 @@ rope_store_general_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, con
     const long long slab_rows = (long long)n_blocks * nkv * bs;
     for (int idx = threadIdx.x; idx < nkv * dv; idx += blockDim.x) {
       const int kvh = idx / dv, e = idx % dv;
-      vpool[((e / ds) * slab_rows + page_row + (long long)kvh * bs) * ds + e % ds] = vsrc[idx];
+      vpool[((e / ds) * slab_rows + page_row + (long long)kvh * bs) * ds + e % ds] =
+          e < dv_src ? vsrc[(size_t)kvh * dv_src + e] : from_f32<T>(0.f);
     }
   }
 }
@@ -228,19 +231,21 @@ CUCA_API int cuca_rope_store_general(void* qkv, int dtype, int ld, int k_col, in
                                      const int* seq_of_row, const int* tables, int table_stride, const float* cos_t,
                                      const float* sin_t, int table_rows, int rot, int pairs, void* kpool, void* vpool,
                                      int n_blocks, int bs, int n_rows, int nh, int nkv, int d, int dv, int v_split,
-                                     int* err, cudaStream_t stream) {
+                                     int dv_src, int* err, cudaStream_t stream) {
   if (n_rows == 0) return 0;
+  if (dv_src <= 0) dv_src = dv;
+  CUCA_REQUIRE(dv_src <= dv, "rope_store: rows with %d values a head do not fit a pool of %d", dv_src, dv);
   CUCA_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "rope_store: rotary size %d does not fit head size %d", rot, d);
   CUCA_REQUIRE(bs > 0 && nh > 0 && nkv >= 0 && d > 0 && dv > 0, "rope_store: bad sizes");
   CUCA_REQUIRE(v_split >= 1 && dv % v_split == 0, "rope_store: %d slabs do not divide value size %d", v_split, dv);
   if (dtype == CUCA_F32)
     cuca_launch(rope_store_general_kernel<float>, dim3(n_rows), dim3(256), 0, stream, true, (float*)qkv, ld, k_col,
                 v_col, positions, seq_of_row, tables, table_stride, cos_t, sin_t, table_rows, rot, pairs, (float*)kpool,
-                (float*)vpool, n_blocks, bs, nh, nkv, d, dv, v_split, err);
+                (float*)vpool, n_blocks, bs, nh, nkv, d, dv, v_split, dv_src, err);
   else if (dtype == CUCA_BF16)
     cuca_launch(rope_store_general_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, true, (__nv_bfloat16*)qkv,
                 ld, k_col, v_col, positions, seq_of_row, tables, table_stride, cos_t, sin_t, table_rows, rot, pairs,
-                (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, n_blocks, bs, nh, nkv, d, dv, v_split, err);
+                (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, n_blocks, bs, nh, nkv, d, dv, v_split, dv_src, err);
   else
     CUCA_REQUIRE(false, "rope_store: unknown dtype %d", dtype);
   CUCA_CHECK_LAUNCH("rope_store_general");
@@ -261,7 +266,7 @@ norm_rope_store_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, TP* __
                        const float* __restrict__ sin_t, int table_rows, int rot, int pairs,
                        const float* __restrict__ q_norm, const float* __restrict__ k_norm, int v_norm, float eps,
                        TP* __restrict__ kpool, TP* __restrict__ vpool, int n_blocks, int bs, int nh, int nkv, int d, int dv,
-                       int v_split, int* err) {
+                       int v_split, int dv_src, int* err) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
@@ -289,7 +294,7 @@ norm_rope_store_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, TP* __
     const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
     if (kind != 0 && page_row < 0) continue;
     const int hh = kind == 0 ? head : (kind == 1 ? head - nh : head - nh - nkv);
-    const int n = kind == 2 ? dv : d;
+    const int n = kind == 2 ? dv_src : d;
     const T* src = base + (kind == 0 ? 0 : (kind == 1 ? k_col : v_col)) + (size_t)hh * n;
     const float* w = kind == 0 ? q_norm : (kind == 1 ? k_norm : nullptr);
     const bool normed = kind == 2 ? v_norm != 0 : w != nullptr;
@@ -303,7 +308,8 @@ norm_rope_store_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, TP* __
     if (kind == 2) {
       const int ds = dv / v_split;
       for (int e = lane; e < dv; e += 32)
-        vpool[((e / ds) * slab_rows + page_row + (long long)hh * bs) * ds + e % ds] = from_f32<TP>(to_f32(src[e]) * inv);
+        vpool[((e / ds) * slab_rows + page_row + (long long)hh * bs) * ds + e % ds] =
+            from_f32<TP>(e < dv_src ? to_f32(src[e]) * inv : 0.f);
       continue;
     }
     TP* dst_p = kind == 1 ? kpool + (page_row + (long long)hh * bs) * d
@@ -335,15 +341,17 @@ CUCA_API int cuca_norm_rope_store(void* qkv, int dtype, int ld, int k_col, int v
                                   const float* cos_t, const float* sin_t, int table_rows, int rot, int pairs,
                                   const float* q_norm, const float* k_norm, int v_norm, float eps, void* kpool,
                                   void* vpool, int n_blocks, int bs, int n_rows, int nh, int nkv, int d, int dv,
-                                  int v_split, int* err, cudaStream_t stream) {
+                                  int v_split, int dv_src, int* err, cudaStream_t stream) {
   if (n_rows == 0) return 0;
+  if (dv_src <= 0) dv_src = dv;
+  CUCA_REQUIRE(dv_src <= dv, "norm_rope_store: rows with %d values a head do not fit a pool of %d", dv_src, dv);
   CUCA_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "norm_rope_store: rotary size %d does not fit head size %d", rot, d);
   CUCA_REQUIRE(bs > 0 && nh > 0 && nkv >= 0 && d > 0 && dv > 0, "norm_rope_store: bad sizes");
   CUCA_REQUIRE(v_split >= 1 && dv % v_split == 0, "norm_rope_store: %d slabs do not divide value size %d", v_split, dv);
 #define NRS(T, TP)                                                                                                    \
   cuca_launch(norm_rope_store_kernel<T, TP>, dim3(n_rows), dim3(256), 0, stream, true, (T*)qkv, ld, k_col, v_col,      \
               (TP*)q_out, positions, seq_of_row, tables, table_stride, cos_t, sin_t, table_rows, rot, pairs, q_norm,   \
-              k_norm, v_norm, eps, (TP*)kpool, (TP*)vpool, n_blocks, bs, nh, nkv, d, dv, v_split, err)
+              k_norm, v_norm, eps, (TP*)kpool, (TP*)vpool, n_blocks, bs, nh, nkv, d, dv, v_split, dv_src, err)
   if (dtype == CUCA_F32 && pool_dtype == CUCA_F32) NRS(float, float);
   else if (dtype == CUCA_BF16 && pool_dtype == CUCA_BF16) NRS(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == CUCA_F32 && pool_dtype == CUCA_BF16) {

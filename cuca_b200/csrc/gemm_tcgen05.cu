@@ -69,6 +69,9 @@ struct Params {
   int ordered_add;  // mode 2 into the 32-bit stream over many tokens: the K slices of a tile add themselves in turn
   int skew;         // ... and slice k + 1 has `skew` K steps more than slice k, so that it finishes when slice k has added
   int slab_rows;    // pairs of CTAs leaving K slices unadded: rows of one slice's slab in `out` (a multiple of 32, >= M)
+  // the gated epilogue: limit <= 0: silu(g) u; limit > 0: g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
+  // u' = clamp(u, -limit, limit)
+  float glu_limit, glu_alpha;
 };
 
 constexpr int STAGING_BUF = 32 * 128;  // 32 rows of 128 bytes
@@ -194,6 +197,14 @@ struct SegmentWalk {
 // for a numerator of zero, which is what every padded row or column of a tile holds, and a warp then pays the slow
 // path for all its lanes (measured: SwiGLU over 255 tokens took 76.7 us, over 256 tokens 63.1).
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+__device__ __forceinline__ float glu_act(const Params& p, float g, float u) {
+  if (p.glu_limit > 0.f) {
+    g = fminf(g, p.glu_limit);
+    u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit);
+    return __fdividef(g, 1.f + __expf(-p.glu_alpha * g)) * (u + 1.f);
+  }
+  return silu_mul(g, u);
+}
 
 // ---- epilogue of 16 accumulator columns held by one thread (TMEM lane `lane_row` of tile rows a0.., columns c..)
 template <int BN, bool DUAL, bool SWAP>
@@ -209,7 +220,7 @@ __device__ __forceinline__ void store16(const Params& p, int a0, int b0, int lan
       const int m = b0 + c + j;
       if (m >= p.M) break;
       const size_t o = (size_t)m * p.ldo + n;
-      if (DUAL) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(silu_mul(v[j], u[j]));
+      if (DUAL) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(glu_act(p, v[j], u[j]));
       else if (p.epilogue == EPI_RESIDUAL) atomicAdd((float*)p.out + o, v[j] + bias);  // result unused: a fire-and-forget
                                                                                        // add; one thread owns the element
       else if (p.out_f32) ((float*)p.out)[o] = v[j] + bias;
@@ -223,7 +234,7 @@ __device__ __forceinline__ void store16(const Params& p, int a0, int b0, int lan
     if (n >= p.N) return;
     float r[16];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) r[j] = DUAL ? silu_mul(v[j], u[j]) : v[j];
+    for (int j = 0; j < 16; ++j) r[j] = DUAL ? glu_act(p, v[j], u[j]) : v[j];
     const size_t o = (size_t)m * p.ldo + n;
     const bool full = n + 16 <= p.N;
     if (!DUAL && p.bias) {
@@ -298,7 +309,7 @@ __device__ __forceinline__ void tma_epilogue(const Params& p, const CUtensorMap*
         float u[16];
         tmem_ld16(acc + 128 + c + h, u);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = silu_mul(v[j], u[j]);
+        for (int j = 0; j < 16; ++j) v[j] = glu_act(p, v[j], u[j]);
       } else if (p.bias && with_bias) {
 #pragma unroll
         for (int j = 0; j < 16; ++j)
@@ -1067,7 +1078,8 @@ CUCA_API void cuca_gemm_pair_mode(int mode) { allow_pair = mode; }
 // (ws_bytes of 32-bit partials; n_counters zeroed ints, left zeroed). max_splits <= 1: whole tiles only.
 static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* out, int out_dtype, int M, int N,
                         int K, int lda, int ldo, int epilogue, void* workspace, size_t ws_bytes, int* counters,
-                        int n_counters, int max_splits, int* n_slices_out, int* err, cudaStream_t stream) {
+                        int n_counters, int max_splits, int* n_slices_out, int* err, cudaStream_t stream,
+                        float glu_limit = 0.f, float glu_alpha = 1.f) {
   if (M == 0 || N == 0) return 0;
   if (!cuca_gemm_tc_supported(A, W, M, N, K, lda)) return 1;
   CUCA_REQUIRE(epilogue != EPI_RESIDUAL || out_dtype == CUCA_F32, "gemm_tc: the residual stream is 32-bit");
@@ -1085,6 +1097,7 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
     Params p;
     p.out = out; p.bias = nullptr; p.workspace = nullptr; p.counters = nullptr; p.err = err;
     p.M = M; p.N = N; p.K = K; p.ldo = N; p.epilogue = EPI_PARTIAL; p.out_f32 = 1;
+    p.glu_limit = 0.f; p.glu_alpha = 1.f;
     p.tile_rows = 2 * TILE_A;
     p.tiles_a = (M + 255) / 256;
     p.tiles = p.tiles_a * ((N + 255) / 256);
@@ -1115,6 +1128,7 @@ static int gemm_tc_impl(const void* A, const void* W, const void* bias, void* ou
   }
   if (!tma_out) tmO = tmA;  // unused
   Params p;
+  p.glu_limit = glu_limit; p.glu_alpha = glu_alpha;
   p.out = out; p.bias = (const __nv_bfloat16*)bias; p.workspace = (float*)workspace; p.counters = counters;
   p.err = err; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.epilogue = epilogue; p.out_f32 = out_dtype == CUCA_F32;
   const int out_cols = swap ? bn : (dual ? 128 : 256);
@@ -1281,6 +1295,17 @@ CUCA_API int cuca_gemm_tc(const void* A, const void* W, const void* bias, void* 
   return gemm_tc_impl(A, W, bias, out, out_dtype, M, N, K, lda, ldo, epilogue, workspace, ws_bytes, counters,
                       n_counters, max_splits, nullptr, err, stream);
 }
+
+// out[M, N] = act(A W^T) for W [2 N, K] = [gate rows; up rows], bf16 out: the gated epilogue with capped inputs,
+// g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit) (limit > 0).
+CUCA_API int cuca_gemm_tc_glu(const void* A, const void* W, void* out, int M, int N, int K, int lda, int ldo,
+                              float limit, float alpha, void* workspace, size_t ws_bytes, int* counters,
+                              int n_counters, int max_splits, int* err, cudaStream_t stream) {
+  CUCA_REQUIRE(limit > 0.f, "gemm_tc_glu: the cap %g is not positive", (double)limit);
+  return gemm_tc_impl(A, W, nullptr, out, CUCA_BF16, M, N, K, lda, ldo, EPI_SWIGLU, workspace, ws_bytes, counters,
+                      n_counters, max_splits, nullptr, err, stream, limit, alpha);
+}
+
 
 CUCA_API int cuca_gemm_tc_partial_max_tokens() { return pair_partial_takes(PAIR_PARTIAL_MAX_TOKENS, 4) ? PAIR_PARTIAL_MAX_TOKENS : SWAP_MAX_TOKENS; }
 

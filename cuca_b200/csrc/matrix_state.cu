@@ -468,25 +468,48 @@ __global__ void mlstm_commit_kernel(const float* __restrict__ nm_new, float* __r
 // o: [rows, H dv] 32-bit. out[r, h, j] = o / sqrt(mean_j o^2 + eps) * w[h * w_head + j] * sigmoid(gate[r, h dv + j]);
 // w_head 0: one weight vector for every head. gate: rows of stride ld_g (TG), null for none.
 template <typename TG, typename TO>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, int w_head,
-                      const TG* __restrict__ gate, int ld_g, TO* __restrict__ out, int H, int dv, float eps) {
-  __shared__ float red[4];
+                      const TG* __restrict__ gate, int ld_g, TO* __restrict__ out, int H, int dv, float eps,
+                      long long n_items) {
   pdl_trigger();
   pdl_wait();
-  const int h = blockIdx.x;
-  const size_t row = blockIdx.y;
-  const float* orow = o + (row * H + h) * dv;
+  // a warp per (row, head); 16 bytes of o a lane at a time where a head's values allow it
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= n_items) return;
+  const size_t row = (size_t)(item / H);
+  const int h = (int)(item % H);
+  const float* orow = o + (size_t)item * dv;
+  const float* wh = w + (size_t)h * w_head;
+  const TG* grow = gate ? gate + row * ld_g + (size_t)h * dv : nullptr;
+  TO* dst = out + (size_t)item * dv;
+  if ((dv & 3) == 0) {
+    float ss = 0.f;
+    for (int j = lane * 4; j < dv; j += 128) {
+      const float4 v = *reinterpret_cast<const float4*>(orow + j);
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    const float inv = 1.f / sqrtf(warp_sum(ss) / (float)dv + eps);
+    for (int j = lane * 4; j < dv; j += 128) {
+      const float4 v = *reinterpret_cast<const float4*>(orow + j);
+      float r[4] = {v.x * inv * wh[j], v.y * inv * wh[j + 1], v.z * inv * wh[j + 2], v.w * inv * wh[j + 3]};
+      if (grow) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) r[e] *= sigmoidf_(to_f32(grow[j + e]));
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dst[j + e] = from_f32<TO>(r[e]);
+    }
+    return;
+  }
   float ss = 0.f;
-  for (int j = threadIdx.x; j < dv; j += 128) ss = fmaf(orow[j], orow[j], ss);
-  ss = warp_sum(ss);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  const float inv = 1.f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)dv + eps);
-  for (int j = threadIdx.x; j < dv; j += 128) {
-    float v = orow[j] * inv * w[(size_t)h * w_head + j];
-    if (gate) v *= sigmoidf_(to_f32(gate[row * ld_g + (size_t)h * dv + j]));
-    out[(row * H + h) * dv + j] = from_f32<TO>(v);
+  for (int j = lane; j < dv; j += 32) ss = fmaf(orow[j], orow[j], ss);
+  const float inv = 1.f / sqrtf(warp_sum(ss) / (float)dv + eps);
+  for (int j = lane; j < dv; j += 32) {
+    float v = orow[j] * inv * wh[j];
+    if (grow) v *= sigmoidf_(to_f32(grow[j]));
+    dst[j] = from_f32<TO>(v);
   }
 }
 
@@ -644,11 +667,11 @@ CUCA_API int cuca_forget_scan(float* proj, int ld, int q_col, int f_col, int v_c
 CUCA_API int cuca_head_norm_gate(const float* o, const float* w, int w_head, const void* gate, int gate_dtype, int ld_g,
                                  void* out, int out_dtype, int n_rows, int H, int dv, float eps, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  CUCA_REQUIRE(n_rows <= 65535, "head_norm_gate: %d rows exceed the launch limit", n_rows);
-  dim3 grid(H, n_rows);
+  const long long n_items = (long long)n_rows * H;
+  dim3 grid((unsigned)((n_items + 7) / 8));
 #define HNG(TG, TO)                                                                                              \
-  cuca_launch(head_norm_gate_kernel<TG, TO>, grid, dim3(128), 0, stream, true, o, w, w_head, (const TG*)gate, ld_g, \
-              (TO*)out, H, dv, eps)
+  cuca_launch(head_norm_gate_kernel<TG, TO>, grid, dim3(256), 0, stream, true, o, w, w_head, (const TG*)gate, ld_g, \
+              (TO*)out, H, dv, eps, n_items)
   if (gate_dtype == CUCA_F32 && out_dtype == CUCA_F32) HNG(float, float);
   else if (gate_dtype == CUCA_F32 && out_dtype == CUCA_BF16) HNG(float, __nv_bfloat16);
   else if (gate_dtype == CUCA_BF16 && out_dtype == CUCA_BF16) HNG(__nv_bfloat16, __nv_bfloat16);

@@ -154,12 +154,51 @@ __global__ void moe_glu_dense_kernel(const T* __restrict__ gu, const float* __re
   }
 }
 
+// The same, 16 bytes a thread (V values of one expert: F, EF and C are multiples of V).
+template <typename T, int V>
+__global__ void moe_glu_dense_vec_kernel(const T* __restrict__ gu, const float* __restrict__ dense, int ld_dense,
+                                         T* __restrict__ a, size_t n_vec, int C, int EF, int F) {
+  pdl_trigger();
+  pdl_wait();
+  const int cv = C / V;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / cv;
+    const int c = (int)(i % cv) * V;
+    const float w = c < EF ? dense[t * ld_dense + c / F] : 1.f;
+    uint4 out4 = make_uint4(0u, 0u, 0u, 0u);
+    if (w != 0.f) {  // (an expert the token did not choose: its rows are not read)
+      const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * C + c);
+      const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * C + C + c);
+      const T* g = reinterpret_cast<const T*>(&g4);
+      const T* u = reinterpret_cast<const T*>(&u4);
+      T* o = reinterpret_cast<T*>(&out4);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const float gv = to_f32(g[e]);
+        o[e] = from_f32<T>(gv / (1.f + expf(-gv)) * to_f32(u[e]) * w);
+      }
+    }
+    *reinterpret_cast<uint4*>(a + t * C + c) = out4;
+  }
+}
+
 // y[t] (+)= ident[t] * h[t]: the experts that return their input.
 template <typename T>
 __global__ void moe_identity_add_kernel(float* __restrict__ y, const T* __restrict__ h, const float* __restrict__ ident,
                                         int store, size_t n, int N) {
   pdl_trigger();
   pdl_wait();
+  if ((N & 3) == 0 && ((uintptr_t)y & 15) == 0) {  // four values a thread
+    const size_t n4 = n / 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+      const float w = ident[(i * 4) / N];
+      float4 v = store ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<const float4*>(y)[i];
+      const T* hv = h + i * 4;
+      v.x += w * to_f32(hv[0]); v.y += w * to_f32(hv[1]); v.z += w * to_f32(hv[2]); v.w += w * to_f32(hv[3]);
+      reinterpret_cast<float4*>(y)[i] = v;
+    }
+    return;
+  }
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const float v = ident[i / N] * to_f32(h[i]);
     y[i] = store ? v : y[i] + v;
@@ -319,9 +358,18 @@ CUCA_API int cuca_moe_glu_dense(const void* gu, const float* dense, int ld_dense
   if (T == 0) return 0;
   CUCA_REQUIRE(F >= 1 && EF % F == 0 && EF <= C && EF / F <= ld_dense, "moe_glu_dense: bad sizes C=%d EF=%d F=%d", C, EF, F);
   const size_t n = (size_t)T * C;
-  size_t blocks = (n + 255) / 256;
-  blocks = blocks > 8192 ? 8192 : blocks;
-  if (dtype == CUCA_F32)
+  const int V = dtype == CUCA_BF16 ? 8 : 4;
+  const bool vec = F % V == 0 && EF % V == 0 && C % V == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)a & 15) == 0;
+  const size_t work = vec ? n / V : n;
+  size_t blocks = (work + 255) / 256;
+  blocks = blocks > 16384 ? 16384 : blocks;
+  if (dtype == CUCA_F32 && vec)
+    cuca_launch(moe_glu_dense_vec_kernel<float, 4>, dim3((unsigned)blocks), dim3(256), 0, stream, true, (const float*)gu,
+                dense, ld_dense, (float*)a, work, C, EF, F);
+  else if (dtype == CUCA_BF16 && vec)
+    cuca_launch(moe_glu_dense_vec_kernel<__nv_bfloat16, 8>, dim3((unsigned)blocks), dim3(256), 0, stream, true,
+                (const __nv_bfloat16*)gu, dense, ld_dense, (__nv_bfloat16*)a, work, C, EF, F);
+  else if (dtype == CUCA_F32)
     cuca_launch(moe_glu_dense_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, true, (const float*)gu, dense,
                 ld_dense, (float*)a, n, C, EF, F);
   else if (dtype == CUCA_BF16)

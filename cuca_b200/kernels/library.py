@@ -55,6 +55,7 @@ _SIGNATURES = {
     "cuca_attention_tc_supported": [_I, _I, _I, _I, _I, _I, _P, _P, _P],
     "cuca_attention_prefill_tc": [_P, _I, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I,
                                   _F, _I, _P, _P],
+    "cuca_gemm_tc_glu": [_P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P, c_size_t, _P, _I, _I, _P, _P],
     "cuca_gemm_tc_partial_slices": [_I, _I, _I, _I],
     "cuca_gemm_tc_partial": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P],
     "cuca_add_partials_rmsnorm": [_P, _P, _I, c_size_t, _P, _P, _I, _P, _I, _I, _F, _P],
@@ -91,7 +92,7 @@ _SIGNATURES = {
                                   _P, _P],
     "cuca_attention_generic_v": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "cuca_rope_store_general": [_P, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I,
-                                _I, _I, _P, _P],
+                                _I, _I, _I, _P, _P],
     "cuca_gate_merge": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
     "cuca_streams_max": [],
     "cuca_spread_streams": [_P, _P, _I, _I, _I, _P],
@@ -117,7 +118,7 @@ _SIGNATURES = {
     "cuca_attention_generic_s": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _F, _I,
                                  _P, _P],
     "cuca_norm_rope_store": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I,
-                             _I, _I, _I, _I, _I, _I, _I, _P, _P],
+                             _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "cuca_forget_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "cuca_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, c_size_t, _P, _I, _I, _P, _P],
 }

@@ -180,6 +180,18 @@ def gemm_tc(a, w, out, epilogue=EPI_STORE, bias=None, err=None, max_splits=16) -
                                    int(max_splits), _p(err), _stream()), "gemm_tc")
 
 
+def gemm_tc_glu(a, w, out, limit: float, alpha: float, err=None, max_splits=16) -> None:
+    """out = g' sigmoid(alpha g') (u' + 1) of [g | u] = a @ w.T (w: gate rows, then up rows), g' = min(g, limit),
+    u' = clamp(u, -limit, limit): the capped gated unit as the contraction's epilogue, from the 32-bit sums."""
+    _cuda(a, w, out)
+    lib = library.load()
+    M, K = a.shape
+    ws, counters = gemm_scratch(a.device)
+    library.check(lib.cuca_gemm_tc_glu(_p(a), _p(w), _p(out), M, out.shape[1], K, a.stride(0), out.stride(0),
+                                       float(limit), float(alpha), _p(ws), ws.numel() * 4, _p(counters),
+                                       counters.numel(), int(max_splits), _p(err), _stream()), "gemm_tc_glu")
+
+
 def gemm_pair_mode(mode: int) -> None:
     """When contractions over many tokens run as pairs of CTAs on one tile (`tcgen05.mma.cta_group::2`): 1 where
     the library's rule expects them to be faster, 0 never, 2 wherever they can (tests and measurements), -1 as the
@@ -813,16 +825,18 @@ def latent_attention(qk, out, cache, step, H, rank, Dk, scale, window, err) -> N
 
 # ------------------------------------------------------------------ attention whose values are wider or narrower than its keys
 def rope_store_general(qkv, k_col, v_col, positions, seq_of_row, tables, cos, sin, rotary_dim, adjacent, kpool, vpool,
-                       block_size, n_heads, n_kv_heads, head_dim, v_head_dim, err, v_split: int = 1) -> None:
+                       block_size, n_heads, n_kv_heads, head_dim, v_head_dim, err, v_split: int = 1,
+                       v_row_dim: int = 0) -> None:
     """Rotate the first `rotary_dim` values of every q head (in place) and k head of `qkv` rows (q heads at column 0,
     k heads at `k_col`, v heads of `v_head_dim` at `v_col`), pairs (i, i + n/2) or, `adjacent`, (2i, 2i + 1); write
-    k and v to the row's page. `v_split` r > 1: the value pool's memory is r slabs of heads r times narrower."""
+    k and v to the row's page. `v_split` r > 1: the value pool's memory is r slabs of heads r times narrower.
+    `v_row_dim` n > 0: a row's value heads hold n values and the pool's `v_head_dim` >= n; the rest is kept as zeros."""
     _cuda(qkv, positions, seq_of_row, kpool, vpool)
     library.check(library.load().cuca_rope_store_general(
         _p(qkv), dtype_code(qkv.dtype), qkv.stride(0), int(k_col), int(v_col), _p(positions), _p(seq_of_row),
         _p(tables), tables.shape[1], _p(cos), _p(sin), cos.shape[0] if cos is not None else 0, int(rotary_dim),
         int(bool(adjacent)), _p(kpool), _p(vpool), kpool.shape[0], int(block_size), qkv.shape[0], n_heads, n_kv_heads,
-        head_dim, v_head_dim, int(v_split), _p(err), _stream()), "rope_store_general")
+        head_dim, v_head_dim, int(v_split), int(v_row_dim), _p(err), _stream()), "rope_store_general")
 
 
 def attention_generic_v(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, n_heads, n_kv_heads,
@@ -839,17 +853,18 @@ def attention_generic_v(q, q_stride, out, kpool, vpool, positions, seq_of_row, t
 
 def norm_rope_store(qkv, k_col, v_col, positions, seq_of_row, tables, cos, sin, rotary_dim, adjacent, q_norm, k_norm,
                     v_norm: bool, eps: float, kpool, vpool, block_size, n_heads, n_kv_heads, head_dim, v_head_dim, err,
-                    v_split: int = 1, q_out=None) -> None:
+                    v_split: int = 1, q_out=None, v_row_dim: int = 0) -> None:
     """`rope_store_general` with norms per head in 32-bit before the rotation: q / rms(q) * q_norm, k likewise with
     k_norm (None: no norm), and with `v_norm` v / rms(v) before it is kept. q is rewritten in place, or goes to
-    `q_out` [rows, heads * head_dim] of the pools' dtype (32-bit rows beside 16-bit pools)."""
+    `q_out` [rows, heads * head_dim] of the pools' dtype (32-bit rows beside 16-bit pools). `v_row_dim` n > 0: a row's
+    value heads hold n values (the norm is over those) and the pool's `v_head_dim` >= n; the rest is kept as zeros."""
     _cuda(qkv, positions, seq_of_row, kpool, vpool, q_norm, k_norm, q_out)
     library.check(library.load().cuca_norm_rope_store(
         _p(qkv), dtype_code(qkv.dtype), qkv.stride(0), int(k_col), int(v_col), _p(q_out), dtype_code(kpool.dtype),
         _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(cos), _p(sin),
         cos.shape[0] if cos is not None else 0, int(rotary_dim), int(bool(adjacent)), _p(q_norm), _p(k_norm),
         int(bool(v_norm)), float(eps), _p(kpool), _p(vpool), kpool.shape[0], int(block_size), qkv.shape[0], n_heads,
-        n_kv_heads, head_dim, v_head_dim, int(v_split), _p(err), _stream()), "norm_rope_store")
+        n_kv_heads, head_dim, v_head_dim, int(v_split), int(v_row_dim), _p(err), _stream()), "norm_rope_store")
 
 
 def sigmoid_gate_(a, gate) -> None:

@@ -20,6 +20,11 @@ Further options of the general path: an RMS norm per head on queries and keys wi
 by the heads (`qk_norm`, before the rotation) and on values without a weight (`v_norm`, before they are kept), a
 smooth cap on the scaled score, c tanh(s / c) (`softcap`), and a sink: one more term exp(0), with no value, in the
 softmax's denominator (`sink`).
+
+Values of a size that is no multiple of the keys' are kept padded with zeros to the next multiple where the
+tensor-core kernels take the rest of the shape (bfloat16, key sizes in steps of 16 up to 128, no output gate): the pool's
+rows, the attention output and the output projection's input columns (zero columns, added at load) are that wide, and
+the layer runs slab by slab like one whose values are a multiple. The norm on values is over the stored ones.
 """
 from __future__ import annotations
 
@@ -74,6 +79,12 @@ class PagedAttention(Mixer):
         if self.general and self.shares_cache:
             raise ValueError("attention: a layer that reads another layer's pages takes neither a value size of its "
                              "own, an output gate, head norms, a score cap, a sink nor adjacent rotation pairs")
+        # the width of a value row in the pool: padded to a multiple of the key size for the tensor-core kernels
+        self.v_pool_dim = self.v_head_dim
+        d, dv = self.head_dim, self.v_head_dim
+        if (self.general and not self.gated and runtime is not None and runtime.dtype == torch.bfloat16 and dv % d
+                and d % 16 == 0 and d <= 128 and -(-dv // d) * d <= 2 * ops.ATTENTION_MAX_HEAD_DIM):
+            self.v_pool_dim = -(-dv // d) * d
         if self.general and not 1 <= self.v_head_dim <= 2 * ops.ATTENTION_MAX_HEAD_DIM:
             raise ValueError(f"attention: value size {self.v_head_dim} is outside what the kernels take "
                              f"(1..{2 * ops.ATTENTION_MAX_HEAD_DIM})")
@@ -81,7 +92,7 @@ class PagedAttention(Mixer):
     # ------------------------------------------------------------ description
     def cache_needs(self):
         return CacheNeeds(kv=KvNeeds(self.n_kv_heads, self.head_dim, self.window,
-                                     None if self.v_head_dim == self.head_dim else self.v_head_dim))
+                                     None if self.v_pool_dim == self.head_dim else self.v_pool_dim))
 
     def tensors(self):
         t, d, dv = self.spec.tensors, self.head_dim, self.v_head_dim
@@ -112,6 +123,11 @@ class PagedAttention(Mixer):
             biases = [b if b is not None else biases[0].new_zeros(get(t[r]).shape[0]) for b, r in zip(biases, roles)]
             self.b_qkv = torch.cat(biases).contiguous()
         self.w_o = get(t["o"])
+        if self.v_pool_dim != self.v_head_dim:  # zero columns where the padded attention output holds zeros
+            w = self.w_o.view(self.width, self.n_heads, self.v_head_dim)
+            wide = w.new_zeros(self.width, self.n_heads, self.v_pool_dim)
+            wide[:, :, :self.v_head_dim] = w
+            self.w_o = wide.view(self.width, self.n_heads * self.v_pool_dim).contiguous()
         self.b_o = get(t["o_bias"]) if "o_bias" in t else None
         if self.qk_norm:
             self.w_qn, self.w_kn = get(t["q_norm"]), get(t["k_norm"])
@@ -135,7 +151,7 @@ class PagedAttention(Mixer):
         as keys: values are r times as wide, the pool is r slabs of heads as wide as the keys, and the kernels run
         once per slab against the same keys. 0: value rows as they are, for the plain kernel. The answer depends on
         the layer's sizes, the compute dtype and the page size alone, so every step lays the pool out alike."""
-        d, dv, bs = self.head_dim, self.v_head_dim, cache.block_size
+        d, dv, bs = self.head_dim, self.v_pool_dim, cache.block_size
         if (self.rt.dtype == torch.bfloat16 and dv % d == 0 and bs & (bs - 1) == 0
                 and ops.attention_mma_supported(self.n_heads, self.n_kv_heads, d, self.w_qkv.shape[0], self.n_heads * d)):
             return dv // d
@@ -145,7 +161,8 @@ class PagedAttention(Mixer):
         """q | k | v | gate in one projection; rotation (either pairing, part of a head) and the page write; attention
         on the tensor cores, once per slab of the values, where the shape allows it, else the plain kernel over value
         rows of their own size; the gate; the output projection."""
-        nh, nkv, d, dv = self.n_heads, self.n_kv_heads, self.head_dim, self.v_head_dim
+        nh, nkv, d, dv = self.n_heads, self.n_kv_heads, self.head_dim, self.v_pool_dim  # (dv: of pool and output)
+        dv_row = self.v_head_dim if dv != self.v_head_dim else 0  # the projection's value heads, where narrower
         rows = h.shape[0]
         proj = self.rt.linear(h, self.w_qkv, bias=self.b_qkv)
         cos, sin, rot, adjacent = self.position.tables() if self.position is not None else (None, None, 0, False)
@@ -159,12 +176,12 @@ class PagedAttention(Mixer):
         if self.normed:
             ops.norm_rope_store(proj, nh * d, (nh + nkv) * d, step.positions, step.seq_of_row, cache.tables, cos, sin,
                                 rot, adjacent, self.w_qn, self.w_kn, self.v_norm, self.eps, cache.k, cache.v,
-                                cache.block_size, nh, nkv, d, dv, self.rt.err, v_split=split)
+                                cache.block_size, nh, nkv, d, dv, self.rt.err, v_split=split, v_row_dim=dv_row)
         else:
             ops.rope_store_general(proj, nh * d, (nh + nkv) * d, step.positions, step.seq_of_row, cache.tables, cos, sin,
                                    rot, adjacent, cache.k, cache.v, cache.block_size, nh, nkv, d, dv, self.rt.err,
-                                   v_split=split)
-        gate = proj[:, (nh + nkv) * d + nkv * dv:] if self.gated else None
+                                   v_split=split, v_row_dim=dv_row)
+        gate = proj[:, (nh + nkv) * d + nkv * dv:] if self.gated else None  # (a gated layer is never padded)
         attn = self.rt.empty(rows, nh * dv)
         if tensor_cores:
             slabs = cache.v.view(split, *cache.k.shape)

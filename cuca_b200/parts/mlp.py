@@ -70,9 +70,13 @@ class CappedGLU(FeedForward):
         return sum(w.numel() * w.element_size() for w in (self.w_gate_up, self.w_down))
 
     def forward(self, h, stream, step) -> None:
-        gu = self.rt.linear(h, self.w_gate_up)
         act = self.rt.empty(h.shape[0], self.inner)
-        ops.glu_capped(gu, act, self.limit, self.alpha)
+        if h.dtype == torch.bfloat16 and ops.gemm_tc_supported(h, self.w_gate_up):
+            # the unit is the contraction's epilogue, from the 32-bit sums (as SwiGLU is in the `swiglu` part)
+            ops.gemm_tc_glu(h, self.w_gate_up, act, self.limit, self.alpha, self.rt.err)
+        else:
+            gu = self.rt.linear(h, self.w_gate_up)
+            ops.glu_capped(gu, act, self.limit, self.alpha)
         self.rt.stream(stream).add_linear(act, self.w_down)
 
 

@@ -109,6 +109,31 @@ def test_capped_unit_alone(rt32, limit):
     assert np.abs(x.cpu().numpy() - want).max() < 2e-5 * max(1.0, np.abs(want).max())
 
 
+@pytest.mark.parametrize("limit", [0.4, 6.0])
+@pytest.mark.parametrize("T", [1, 9, 64, 65, 200, 700])
+def test_capped_unit_as_the_contraction_epilogue(limit, T):
+    """In the serving precision the unit is computed inside the gate/up contraction, from its 32-bit sums, whichever
+    tiling the number of tokens selects; sizes that are no multiple of a tile."""
+    from cuca_b200.parts.base import PartSpec
+    from cuca_b200.parts.mlp import CappedGLU
+    from cuca_b200.runtime import Runtime
+    rt = Runtime("cuda:0", torch.bfloat16)
+    dev, E, F = rt.device, 72, 200
+    part = CappedGLU(PartSpec("glu_capped", {"width": E, "inner": F, "limit": limit},
+                              {"gate": "gate", "up": "up", "down": "down"}), rt)
+    rs = np.random.default_rng(T)
+    ws = {k: pu.bf16_round(v) for k, v in (("gate", rs.normal(0, 1, (F, E)) / np.sqrt(E)),
+                                           ("up", rs.normal(0, 1, (F, E)) / np.sqrt(E)),
+                                           ("down", rs.normal(0, 1, (E, F)) / np.sqrt(F)))}
+    part.load(lambda name: torch.tensor(ws[name], dtype=torch.bfloat16, device=dev))
+    f = pu.bf16_round(rs.normal(0, 2.0, (T, E)))
+    want = pp.capped_glu(f, ws, "", limit)
+    stream = rt.stream(torch.zeros(T, E, device=dev))
+    part.forward(torch.tensor(f, dtype=torch.bfloat16, device=dev), stream, None)
+    assert np.abs(stream.data.cpu().numpy() - want).max() < 2e-2 * max(1.0, np.abs(want).max())
+    assert int(rt.err.item()) == 0
+
+
 @pytest.mark.parametrize("layer", [pu.hg(), pu.hg(heads=1, dim=40, vdim=8), pu.hg(heads=2, dim=128, vdim=96),
                                    pu.hg(heads=5, dim=4, vdim=36), pu.hg(heads=1, dim=7, vdim=150),
                                    pu.hg(heads=2, dim=200, vdim=5)])
@@ -262,7 +287,7 @@ def test_one_far_key_that_matters(dtype, dim, vdim, softcap):
     rs = np.random.default_rng(3)
     for cuts in ([1000], [n - 14] + [1] * 20, [5, 2, 300, 2, 1000]):
         kpool = torch.zeros((70, 1, bs, dim), dtype=dtype, device=dev)
-        vpool = torch.zeros((70, 1, bs, vdim), dtype=dtype, device=dev)
+        vpool = torch.zeros((70, 1, bs, part.v_pool_dim), dtype=dtype, device=dev)  # (padded in bfloat16)
         tables = torch.full((4, 64), -1, dtype=torch.int32, device=dev)
         tables[1, :63] = torch.tensor(rs.permutation(70)[:63].tolist(), dtype=torch.int32)
 
@@ -292,7 +317,7 @@ def test_the_sink_takes_the_weight_when_no_key_fits(dtype, dim, vdim):
     assert np.abs(want[25:]).max() < 1e-3 * no_sink_scale and np.abs(o).max() > 0
     for cuts in ([1000], [22] + [1] * 30):
         kpool = torch.zeros((8, 1, bs, dim), dtype=dtype, device=dev)
-        vpool = torch.zeros((8, 1, bs, vdim), dtype=dtype, device=dev)
+        vpool = torch.zeros((8, 1, bs, part.v_pool_dim), dtype=dtype, device=dev)
         tables = torch.full((4, 8), -1, dtype=torch.int32, device=dev)
         tables[3, :6] = torch.tensor([4, 1, 7, 0, 2, 5], dtype=torch.int32)
 
