@@ -271,7 +271,9 @@ __global__ void forget_scan_kernel(const float* __restrict__ proj, int ld, int q
     const float* tok = sm + (size_t)(c & 1) * TC * per;
     float* po_at = out + (size_t)(r0 + t0) * H * dv + (size_t)h * dv + col;
     const int mine = s * staged_stride<NR>();
-#pragma unroll 2
+    // (tokens depend on each other through the state's one multiply-add alone: with four rows a thread, eight
+    // tokens in flight keep the loads and the shuffled sums of the next ones going while these wait)
+#pragma unroll(NR == 4 ? 8 : 2)
     for (int t = 0; t < nt; ++t, tok += per, po_at += H * dv) {
       const float4* gq = reinterpret_cast<const float4*>(tok + mine);
       const float4* gf = reinterpret_cast<const float4*>(tok + dpp + mine);
