@@ -28,7 +28,7 @@ def architectures() -> list[str]:
 
 
 def _ensure_builtin() -> None:
-    from ..models import bananex, dupenex, llama, pudinex  # noqa: F401  (they register themselves)
+    from ..models import bananex, dupenex, llama, pudinex, sutosun  # noqa: F401  (they register themselves)
 
 
 def build_spec(config_json: dict):

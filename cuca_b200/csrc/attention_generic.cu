@@ -16,7 +16,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const T* __restrict__ kpool, const T* __restrict__ vpool, int n_blocks, int bs,
                          const int* __restrict__ positions, const int* __restrict__ seq_of_row,
                          const int* __restrict__ tables, int table_stride, int nh, int nkv, int d, int dv,
-                         float scale, int window, float softcap, int sink, int* err) {
+                         float scale, int window, float softcap, int sink, const float* __restrict__ sink_val,
+                         int* err) {
   extern __shared__ float qs[];  // [4][d]
   pdl_trigger();
   pdl_wait();
@@ -81,10 +82,11 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     }
     m = m_new;
   }
-  if (sink) {  // one more term in the denominator: a key of score 0 that has no value
-    const float m_new = fmaxf(m, 0.f);
+  if (sink) {  // one more term in the denominator: a key of score 0 (or of the head's stored score) that has no value
+    const float s0 = sink_val ? sink_val[head] : 0.f;
+    const float m_new = fmaxf(m, s0);
     const float corr = expf(m - m_new);
-    l = l * corr + expf(-m_new);
+    l = l * corr + expf(s0 - m_new);
 #pragma unroll
     for (int c = 0; c < VC; ++c) acc[c] *= corr;
   }
@@ -108,12 +110,14 @@ CUCA_API int cuca_attention_max_head_dim() { return 256; }
 // heads; out: [n_rows, out_stride] with nh heads of dv values; key pool [n_blocks][nkv][bs][d], value pool
 // [n_blocks][nkv][bs][dv]. Row r is at position positions[r] of sequence seq_of_row[r] (< 0: padding, skipped) and
 // sees keys max(0, P - window + 1)..P of that sequence (window 0: all). softcap c > 0: a score s becomes
-// c tanh(s / c). sink: the softmax's denominator holds one more term, exp(0).
-CUCA_API int cuca_attention_generic_s(const void* q, int q_stride, void* out, int out_stride, int dtype,
+// c tanh(s / c). sink: the softmax's denominator holds one more term, exp(0), or with sink_val (32-bit, one number per
+// query head) exp(sink_val[head]): a score that is neither scaled nor capped.
+CUCA_API int cuca_attention_generic_sv(const void* q, int q_stride, void* out, int out_stride, int dtype,
                                       const void* kpool, const void* vpool, int n_blocks, int bs,
                                       const int* positions, const int* seq_of_row, const int* tables,
                                       int table_stride, int n_rows, int nh, int nkv, int d, int dv, float scale,
-                                      int window, float softcap, int sink, int* err, cudaStream_t stream) {
+                                      int window, float softcap, int sink, const float* sink_val, int* err,
+                                      cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(d > 0 && d <= cuca_attention_max_head_dim(), "attention: head size %d is outside 1..%d", d, cuca_attention_max_head_dim());
   CUCA_REQUIRE(dv > 0 && dv <= 2 * cuca_attention_max_head_dim(), "attention: value size %d is outside 1..%d", dv,
@@ -125,7 +129,7 @@ CUCA_API int cuca_attention_generic_s(const void* q, int q_stride, void* out, in
 #define AG(T, VC)                                                                                                  \
   cuca_launch(attention_generic_kernel<T, VC>, grid, dim3(128), smem, stream, true, (const T*)q, q_stride, (T*)out, \
               out_stride, (const T*)kpool, (const T*)vpool, n_blocks, bs, positions, seq_of_row, tables,            \
-              table_stride, nh, nkv, d, dv, scale, window, softcap, sink, err)
+              table_stride, nh, nkv, d, dv, scale, window, softcap, sink, sink_val, err)
   if (dtype == CUCA_F32) {
     if (dv <= 256) AG(float, 8); else AG(float, 16);
   } else if (dtype == CUCA_BF16) {
@@ -136,6 +140,16 @@ CUCA_API int cuca_attention_generic_s(const void* q, int q_stride, void* out, in
 #undef AG
   CUCA_CHECK_LAUNCH("attention_generic");
   return 0;
+}
+
+CUCA_API int cuca_attention_generic_s(const void* q, int q_stride, void* out, int out_stride, int dtype,
+                                      const void* kpool, const void* vpool, int n_blocks, int bs,
+                                      const int* positions, const int* seq_of_row, const int* tables,
+                                      int table_stride, int n_rows, int nh, int nkv, int d, int dv, float scale,
+                                      int window, float softcap, int sink, int* err, cudaStream_t stream) {
+  return cuca_attention_generic_sv(q, q_stride, out, out_stride, dtype, kpool, vpool, n_blocks, bs, positions, seq_of_row,
+                                  tables, table_stride, n_rows, nh, nkv, d, dv, scale, window, softcap, sink, nullptr,
+                                  err, stream);
 }
 
 CUCA_API int cuca_attention_generic_v(const void* q, int q_stride, void* out, int out_stride, int dtype,
@@ -257,6 +271,10 @@ CUCA_API int cuca_rope_store_general(void* qkv, int dtype, int ld, int k_col, in
 // k_norm; a null weight: no norm), and with v_norm a v head becomes v / rms(v) (no weight) before it is kept. T is the
 // rows' type (a 32-bit projection result may feed 16-bit pools: TP); q is written in place when q_out is null, else to
 // q_out [rows, nh d] of the pools' type. A warp per head.
+// whole != 0: the norm is over the whole projection instead, all heads at once: q / rms(q over its nh d values) times
+// q_norm [nh d], k alike over its nkv d values with k_norm [nkv d] (v_norm is not combined with it).
+// qt_every > 0: the query of a row at position p is multiplied by 1 + qt_coef ln(floor((p + 1) / qt_every) + 1), after
+// norm and rotation.
 namespace {
 template <typename T, typename TP>
 __global__ void __launch_bounds__(256)
@@ -266,7 +284,8 @@ norm_rope_store_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, TP* __
                        const float* __restrict__ sin_t, int table_rows, int rot, int pairs,
                        const float* __restrict__ q_norm, const float* __restrict__ k_norm, int v_norm, float eps,
                        TP* __restrict__ kpool, TP* __restrict__ vpool, int n_blocks, int bs, int nh, int nkv, int d, int dv,
-                       int v_split, int dv_src, int* err) {
+                       int v_split, int dv_src, int whole, float qt_coef, int qt_every, int* err) {
+  __shared__ float red[2][8];
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
@@ -276,6 +295,21 @@ norm_rope_store_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, TP* __
   const int half = rot / 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
   T* base = qkv + (size_t)row * ld;
+  float inv_whole[2] = {1.f, 1.f};  // of q and of k, when the norm is over the whole projection
+  if (whole) {
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nh * d; i += blockDim.x) { const float v = to_f32(base[i]); sq = fmaf(v, v, sq); }
+    for (int i = threadIdx.x; i < nkv * d; i += blockDim.x) { const float v = to_f32(base[k_col + i]); sk = fmaf(v, v, sk); }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; }
+    __syncthreads();  // (also: every value is read before any thread rewrites q in place)
+    float tq = 0.f, tk = 0.f;
+    for (int i = 0; i < n_warps; ++i) { tq += red[0][i]; tk += red[1][i]; }
+    inv_whole[0] = 1.f / sqrtf(tq / (float)(nh * d) + eps);
+    if (nkv > 0) inv_whole[1] = 1.f / sqrtf(tk / (float)(nkv * d) + eps);
+  }
+  const float q_mul = (qt_every > 0 && pos >= 0) ? 1.f + qt_coef * logf((float)((pos + 1) / qt_every + 1)) : 1.f;
   long long page_row = -1;
   if (nkv > 0) {
     int blk = pos >= 0 ? tables[(size_t)seq * table_stride + pos / bs] : -1;
@@ -297,8 +331,10 @@ norm_rope_store_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, TP* __
     const int n = kind == 2 ? dv_src : d;
     const T* src = base + (kind == 0 ? 0 : (kind == 1 ? k_col : v_col)) + (size_t)hh * n;
     const float* w = kind == 0 ? q_norm : (kind == 1 ? k_norm : nullptr);
-    const bool normed = kind == 2 ? v_norm != 0 : w != nullptr;
-    float inv = 1.f;
+    if (whole && w) w += (size_t)hh * d;  // the weight covers the whole projection
+    const bool normed = kind == 2 ? v_norm != 0 : (w != nullptr && !whole);
+    float inv = (whole && kind != 2) ? inv_whole[kind] : 1.f;
+    const float mul = kind == 0 ? q_mul : 1.f;
     if (normed) {
       float ss = 0.f;
       for (int i = lane; i < n; i += 32) { const float v = to_f32(src[i]); ss = fmaf(v, v, ss); }
@@ -324,11 +360,11 @@ norm_rope_store_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, TP* __
         const int ia = pairs ? 2 * i : i, ib = pairs ? 2 * i + 1 : i + half;
         const float c = in_table ? cr[i] : 1.f, sn = in_table ? sr[i] : 0.f;
         const float a = to_f32(src[ia]) * inv * (w ? w[ia] : 1.f), b = to_f32(src[ib]) * inv * (w ? w[ib] : 1.f);
-        put(ia, a * c - b * sn);
-        put(ib, b * c + a * sn);
+        put(ia, (a * c - b * sn) * mul);
+        put(ib, (b * c + a * sn) * mul);
       } else {
         const int e = rot + (i - half);
-        put(e, to_f32(src[e]) * inv * (w ? w[e] : 1.f));
+        put(e, to_f32(src[e]) * inv * (w ? w[e] : 1.f) * mul);
       }
     }
   }
@@ -336,13 +372,17 @@ norm_rope_store_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, TP* __
 }  // namespace
 
 // dtype: of the rows; pool_dtype: of the pools and of q_out (null: q in place, in the rows' type).
-CUCA_API int cuca_norm_rope_store(void* qkv, int dtype, int ld, int k_col, int v_col, void* q_out, int pool_dtype,
-                                  const int* positions, const int* seq_of_row, const int* tables, int table_stride,
-                                  const float* cos_t, const float* sin_t, int table_rows, int rot, int pairs,
-                                  const float* q_norm, const float* k_norm, int v_norm, float eps, void* kpool,
-                                  void* vpool, int n_blocks, int bs, int n_rows, int nh, int nkv, int d, int dv,
-                                  int v_split, int dv_src, int* err, cudaStream_t stream) {
+// whole, qt_coef, qt_every: see the kernel (0, 0, 0: norms per head, no query temperature).
+CUCA_API int cuca_norm_rope_store_w(void* qkv, int dtype, int ld, int k_col, int v_col, void* q_out, int pool_dtype,
+                                    const int* positions, const int* seq_of_row, const int* tables, int table_stride,
+                                    const float* cos_t, const float* sin_t, int table_rows, int rot, int pairs,
+                                    const float* q_norm, const float* k_norm, int v_norm, float eps, void* kpool,
+                                    void* vpool, int n_blocks, int bs, int n_rows, int nh, int nkv, int d, int dv,
+                                    int v_split, int dv_src, int whole, float qt_coef, int qt_every, int* err,
+                                    cudaStream_t stream) {
   if (n_rows == 0) return 0;
+  CUCA_REQUIRE(!whole || (q_norm && (nkv == 0 || k_norm) && !v_norm),
+               "norm_rope_store: a norm over the whole projection needs both weights and takes no value norm");
   if (dv_src <= 0) dv_src = dv;
   CUCA_REQUIRE(dv_src <= dv, "norm_rope_store: rows with %d values a head do not fit a pool of %d", dv_src, dv);
   CUCA_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "norm_rope_store: rotary size %d does not fit head size %d", rot, d);
@@ -351,7 +391,8 @@ CUCA_API int cuca_norm_rope_store(void* qkv, int dtype, int ld, int k_col, int v
 #define NRS(T, TP)                                                                                                    \
   cuca_launch(norm_rope_store_kernel<T, TP>, dim3(n_rows), dim3(256), 0, stream, true, (T*)qkv, ld, k_col, v_col,      \
               (TP*)q_out, positions, seq_of_row, tables, table_stride, cos_t, sin_t, table_rows, rot, pairs, q_norm,   \
-              k_norm, v_norm, eps, (TP*)kpool, (TP*)vpool, n_blocks, bs, nh, nkv, d, dv, v_split, dv_src, err)
+              k_norm, v_norm, eps, (TP*)kpool, (TP*)vpool, n_blocks, bs, nh, nkv, d, dv, v_split, dv_src, whole,       \
+              qt_coef, qt_every, err)
   if (dtype == CUCA_F32 && pool_dtype == CUCA_F32) NRS(float, float);
   else if (dtype == CUCA_BF16 && pool_dtype == CUCA_BF16) NRS(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == CUCA_F32 && pool_dtype == CUCA_BF16) {
@@ -361,4 +402,15 @@ CUCA_API int cuca_norm_rope_store(void* qkv, int dtype, int ld, int k_col, int v
 #undef NRS
   CUCA_CHECK_LAUNCH("norm_rope_store");
   return 0;
+}
+
+CUCA_API int cuca_norm_rope_store(void* qkv, int dtype, int ld, int k_col, int v_col, void* q_out, int pool_dtype,
+                                  const int* positions, const int* seq_of_row, const int* tables, int table_stride,
+                                  const float* cos_t, const float* sin_t, int table_rows, int rot, int pairs,
+                                  const float* q_norm, const float* k_norm, int v_norm, float eps, void* kpool,
+                                  void* vpool, int n_blocks, int bs, int n_rows, int nh, int nkv, int d, int dv,
+                                  int v_split, int dv_src, int* err, cudaStream_t stream) {
+  return cuca_norm_rope_store_w(qkv, dtype, ld, k_col, v_col, q_out, pool_dtype, positions, seq_of_row, tables,
+                                table_stride, cos_t, sin_t, table_rows, rot, pairs, q_norm, k_norm, v_norm, eps, kpool,
+                                vpool, n_blocks, bs, n_rows, nh, nkv, d, dv, v_split, dv_src, 0, 0.f, 0, err, stream);
 }

@@ -47,7 +47,8 @@ struct AttnParams {
   float scale_log2e;
   float cap_log2e;       // > 0: a score s becomes cap tanh(s / cap); this is cap log2(e), and ...
   float cap_arg;         // ... 2 scale log2(e) / cap: exp2(raw cap_arg) = e^(2 s / cap)
-  int sink;              // 1: the softmax's denominator holds one more exp(0)
+  int sink;              // 1: the softmax's denominator holds one more exp(0) ...
+  const float* sink_val; // ... or, when given, exp(sink_val[query head]) (32-bit; neither scaled nor capped)
   int window;
   int chunk;             // decode: key positions per split (multiple of 64); 0: each row divides its own length
   int slots;             // decode, chunk 0: CTAs the GPU holds at once (for the choice of chunks per row)
@@ -146,8 +147,11 @@ __device__ __forceinline__ float score_log2(float raw, const AttnParams& p) {
   if (p.cap_log2e > 0.f) return p.cap_log2e - __fdividef(2.f * p.cap_log2e, exp2f(raw * p.cap_arg) + 1.f);
   return raw * p.scale_log2e;
 }
-// What a sink (score 0, no value) adds to a row sum kept relative to the maximum m (log2 units)
-__device__ __forceinline__ float sink_term(float m) { return m == -INFINITY ? 1.f : exp2f(-m); }
+// What a sink (score 0 or the head's stored score, no value) adds to a row sum kept relative to the maximum m (log2 units)
+__device__ __forceinline__ float sink_term(float m, const AttnParams& p, int head) {
+  if (m == -INFINITY) return 1.f;  // a row without keys: its sums are 0 and so is its output
+  return exp2f((p.sink_val ? p.sink_val[head] * 1.4426950408889634f : 0.f) - m);
+}
 
 template <int D, bool DECODE, bool FUSED, bool TMA>
 __global__ void __launch_bounds__(NTHREADS)
@@ -717,7 +721,7 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       if (!row_ok[h]) continue;
-      if (p.sink) st.l[h] += sink_term(st.m[h]);
+      if (p.sink) st.l[h] += sink_term(st.m[h], p, row_head[h]);
       float inv = st.l[h] > 0.f ? 1.f / st.l[h] : 0.f;
       __nv_bfloat16* o = p.out + (size_t)row_token[h] * p.out_stride + (size_t)row_head[h] * D;
 #pragma unroll
@@ -767,7 +771,7 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
       O += src[dim] * f;
     }
     if (n_used == 1) {
-      if (p.sink) L += sink_term(M);
+      if (p.sink) L += sink_term(M, p, kvh * G + item);
       p.out[(size_t)dec_row * p.out_stride + (size_t)(kvh * G + item) * D + dim] =
           __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
     } else {
@@ -808,7 +812,7 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
           L += s_f[item][sidx] * f;
           s_f[item][sidx] = f;
         }
-        if (p.sink) L += sink_term(M);
+        if (p.sink) L += sink_term(M, p, kvh * G + item);
         s_inv[item] = L > 0.f ? 1.f / L : 0.f;
       }
       __syncthreads();
@@ -874,7 +878,7 @@ attn_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmK, con
       L += s_f[item][sidx] * f;
       s_f[item][sidx] = f;
     }
-    if (p.sink) L += sink_term(M);
+    if (p.sink) L += sink_term(M, p, kvh * G + item);
     s_inv[item] = L > 0.f ? 1.f / L : 0.f;
   }
   __syncthreads();
@@ -985,17 +989,19 @@ struct FusedInput {
   int table_rows, rot, has_kv;
 };
 
-void set_score_options(AttnParams& p, float scale, float softcap, int sink) {
+void set_score_options(AttnParams& p, float scale, float softcap, int sink, const float* sink_val = nullptr) {
   p.cap_log2e = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
   p.cap_arg = softcap > 0.f ? 2.f * scale * 1.4426950408889634f / softcap : 0.f;
   p.sink = sink ? 1 : 0;
+  p.sink_val = sink ? sink_val : nullptr;
 }
 
 int attention_decode_impl(const void* q, int q_stride, const FusedInput* fused, void* out, int out_stride,
                           const void* kpool, const void* vpool, int n_blocks, int bs, const int* positions,
                           const int* seq_of_row, const int* tables, int table_stride, const int* rows, int n_rows,
                           int nh, int nkv, int d, float scale, int window, int chunk, int n_splits, float* part,
-                          int* counters, int* err, cudaStream_t stream, float softcap = 0.f, int sink = 0) {
+                          int* counters, int* err, cudaStream_t stream, float softcap = 0.f, int sink = 0,
+                          const float* sink_val = nullptr) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -1020,7 +1026,7 @@ int attention_decode_impl(const void* q, int q_stride, const FusedInput* fused, 
   p.rows = rows; p.tile_row0 = nullptr; p.tile_nrows = nullptr; p.nh = nh; p.nkv = nkv;
   p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.chunk = chunk; p.part = part;
   p.counters = counters; p.err = err; p.slots = sms * per_sm;
-  set_score_options(p, scale, softcap, sink);
+  set_score_options(p, scale, softcap, sink, sink_val);
   p.cluster = by_cluster ? 1 : 0;
   p.partial = nullptr; p.n_slices = 0; p.slice_stride = 0; p.bias = nullptr; p.cos_t = p.sin_t = nullptr;
   p.table_rows = 0; p.rot = 0; p.has_kv = 0;
@@ -1056,16 +1062,28 @@ CUCA_API int cuca_attention_decode(const void* q, int q_stride, void* out, int o
 }
 
 // The decode form with a smooth cap on the scaled scores (softcap c > 0: s becomes c tanh(s / c)) and, with `sink`, one
-// more term exp(0) without a value in every row's denominator.
+// more term without a value in every row's denominator: exp(0), or exp(sink_val[query head]) when sink_val (32-bit,
+// one number per query head, neither scaled nor capped) is given.
+CUCA_API int cuca_attention_decode_sv(const void* q, int q_stride, void* out, int out_stride, const void* kpool,
+                                      const void* vpool, int n_blocks, int bs, const int* positions,
+                                      const int* seq_of_row, const int* tables, int table_stride, const int* rows,
+                                      int n_rows, int nh, int nkv, int d, float scale, int window, float softcap,
+                                      int sink, const float* sink_val, int chunk, int n_splits, float* part,
+                                      int* counters, int* err, cudaStream_t stream) {
+  return attention_decode_impl(q, q_stride, nullptr, out, out_stride, kpool, vpool, n_blocks, bs, positions,
+                               seq_of_row, tables, table_stride, rows, n_rows, nh, nkv, d, scale, window, chunk,
+                               n_splits, part, counters, err, stream, softcap, sink, sink_val);
+}
+
 CUCA_API int cuca_attention_decode_s(const void* q, int q_stride, void* out, int out_stride, const void* kpool,
                                      const void* vpool, int n_blocks, int bs, const int* positions,
                                      const int* seq_of_row, const int* tables, int table_stride, const int* rows,
                                      int n_rows, int nh, int nkv, int d, float scale, int window, float softcap,
                                      int sink, int chunk, int n_splits, float* part, int* counters, int* err,
                                      cudaStream_t stream) {
-  return attention_decode_impl(q, q_stride, nullptr, out, out_stride, kpool, vpool, n_blocks, bs, positions,
-                               seq_of_row, tables, table_stride, rows, n_rows, nh, nkv, d, scale, window, chunk,
-                               n_splits, part, counters, err, stream, softcap, sink);
+  return cuca_attention_decode_sv(q, q_stride, out, out_stride, kpool, vpool, n_blocks, bs, positions, seq_of_row, tables,
+                                  table_stride, rows, n_rows, nh, nkv, d, scale, window, softcap, sink, nullptr, chunk,
+                                  n_splits, part, counters, err, stream);
 }
 
 // The decode form fed by the unadded K slices of the stacked q/k/v projection, partial[slice][row][(nh + 2 nkv) d]
@@ -1088,11 +1106,12 @@ CUCA_API int cuca_attention_decode_fused(const float* partial, int n_slices, siz
 
 // Prefill form: tile i covers rows tile_row0[i] .. +tile_nrows[i]-1 (at most 64 consecutive rows of one request).
 // (softcap and sink as in the decode form)
-CUCA_API int cuca_attention_prefill_s(const void* q, int q_stride, void* out, int out_stride, const void* kpool,
-                                      const void* vpool, int n_blocks, int bs, const int* positions,
-                                      const int* seq_of_row, const int* tables, int table_stride,
-                                      const int* tile_row0, const int* tile_nrows, int n_tiles, int nh, int nkv, int d,
-                                      float scale, int window, float softcap, int sink, int* err, cudaStream_t stream) {
+CUCA_API int cuca_attention_prefill_sv(const void* q, int q_stride, void* out, int out_stride, const void* kpool,
+                                       const void* vpool, int n_blocks, int bs, const int* positions,
+                                       const int* seq_of_row, const int* tables, int table_stride,
+                                       const int* tile_row0, const int* tile_nrows, int n_tiles, int nh, int nkv, int d,
+                                       float scale, int window, float softcap, int sink, const float* sink_val,
+                                       int* err, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   CUCA_REQUIRE(cuca_attention_mma_supported(nh, nkv, d, q_stride, out_stride), "attention_prefill: unsupported "
                "shape (heads %d/%d, head size %d)", nh, nkv, d);
@@ -1105,10 +1124,20 @@ CUCA_API int cuca_attention_prefill_s(const void* q, int q_stride, void* out, in
   p.rows = nullptr; p.tile_row0 = tile_row0; p.tile_nrows = tile_nrows; p.nh = nh; p.nkv = nkv;
   p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.chunk = 0; p.part = nullptr;
   p.counters = nullptr; p.err = err; p.slots = 1; p.cluster = 0;
-  set_score_options(p, scale, softcap, sink);
+  set_score_options(p, scale, softcap, sink, sink_val);
   p.partial = nullptr; p.n_slices = 0; p.slice_stride = 0; p.bias = nullptr; p.cos_t = p.sin_t = nullptr;
   p.table_rows = 0; p.rot = 0; p.has_kv = 0;
   return dispatch<false, false>(d, p, dim3(n_tiles, nh), stream);
+}
+
+CUCA_API int cuca_attention_prefill_s(const void* q, int q_stride, void* out, int out_stride, const void* kpool,
+                                      const void* vpool, int n_blocks, int bs, const int* positions,
+                                      const int* seq_of_row, const int* tables, int table_stride,
+                                      const int* tile_row0, const int* tile_nrows, int n_tiles, int nh, int nkv, int d,
+                                      float scale, int window, float softcap, int sink, int* err, cudaStream_t stream) {
+  return cuca_attention_prefill_sv(q, q_stride, out, out_stride, kpool, vpool, n_blocks, bs, positions, seq_of_row,
+                                   tables, table_stride, tile_row0, tile_nrows, n_tiles, nh, nkv, d, scale, window,
+                                   softcap, sink, nullptr, err, stream);
 }
 
 CUCA_API int cuca_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* kpool,

@@ -62,7 +62,8 @@ struct Params {
   float scale_log2e;
   float cap_log2e;       // > 0: a score s becomes cap tanh(s / cap); this is cap log2(e), and ...
   float cap_arg;         // ... 2 scale log2(e) / cap: exp2(raw cap_arg) = e^(2 s / cap)
-  int sink;              // 1: the denominator holds one more exp(0)
+  int sink;              // 1: the denominator holds one more exp(0) ...
+  const float* sink_val; // ... or, when given, exp(sink_val[query head]) (32-bit, neither scaled nor capped)
   int window;
   int* err;
 };
@@ -489,7 +490,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     if (ok && __all_sync(0xffffffffu, mbar_wait(&pv_done[x], (n_tiles - 1) & 1, p.err, abort_flag))) {
       tc_fence_after();
-      if (p.sink) l += (m == -INFINITY) ? 1.f : fast_exp2(-m);  // the sink's score is 0; m is the reference in log2 units
+      // the sink's score is 0 or the head's stored number; m is the reference in log2 units
+      if (p.sink)
+        l += (m == -INFINITY) ? 1.f : fast_exp2((p.sink_val ? p.sink_val[head0 + x] * 1.4426950408889634f : 0.f) - m);
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* dst = p.out + (size_t)(row0 + r) * p.out_stride + (size_t)(head0 + x) * D;
 #pragma unroll
@@ -562,12 +565,14 @@ CUCA_API void cuca_attention_pair_tiles_mode(int mode) { pair_mode = mode; }
 
 // Prefill form on tcgen05: tile i covers rows tile_row0[i] .. +tile_nrows[i]-1 (at most 128 consecutive rows of
 // one request). q: [n_rows_total][q_stride] with the rotated query heads first; out: [..][out_stride].
-CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_total, void* out, int out_stride,
-                                       const void* kpool, const void* vpool, int n_blocks, int bs,
-                                       const int* positions, const int* seq_of_row, const int* tables,
-                                       int table_stride, const int* tile_row0, const int* tile_nrows, int n_tiles,
-                                       int nh, int nkv, int d, float scale, int window, float softcap, int sink,
-                                       int* err, cudaStream_t stream) {
+// sink: one more term without a value in every row's denominator, exp(0) or, with sink_val (32-bit, one number per
+// query head), exp(sink_val[head]).
+CUCA_API int cuca_attention_prefill_tc_sv(const void* q, int q_stride, int n_rows_total, void* out, int out_stride,
+                                          const void* kpool, const void* vpool, int n_blocks, int bs,
+                                          const int* positions, const int* seq_of_row, const int* tables,
+                                          int table_stride, const int* tile_row0, const int* tile_nrows, int n_tiles,
+                                          int nh, int nkv, int d, float scale, int window, float softcap, int sink,
+                                          const float* sink_val, int* err, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   CUCA_REQUIRE(cuca_attention_tc_supported(nh, nkv, d, bs, q_stride, out_stride, q, kpool, vpool),
                "attention_prefill_tc: unsupported shape (heads %d/%d, head size %d, page %d)", nh, nkv, d, bs);
@@ -585,6 +590,7 @@ CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_t
   p.cap_log2e = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
   p.cap_arg = softcap > 0.f ? 2.f * scale * 1.4426950408889634f / softcap : 0.f;
   p.sink = sink ? 1 : 0;
+  p.sink_val = sink ? sink_val : nullptr;
   p.heads_per_cta = ((nh / nkv) % NQ == 0) ? NQ : 1;
   p.n_tiles = n_tiles;
   // Two tiles per CTA, a heavy and a light one, where that makes one round of CTAs out of more than one
@@ -594,4 +600,15 @@ CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_t
   p.pair_tiles = n_tiles >= 2 && (pair_mode == 2 || (pair_mode == 1 && n_tiles * head_ctas > sms &&
                                                      ((n_tiles + 1) / 2) * head_ctas <= sms)) ? 1 : 0;
   return d == 128 ? launch_attn_tc<128>(tmQ, tmK, tmV, p, n_tiles, stream) : launch_attn_tc<64>(tmQ, tmK, tmV, p, n_tiles, stream);
+}
+
+CUCA_API int cuca_attention_prefill_tc(const void* q, int q_stride, int n_rows_total, void* out, int out_stride,
+                                       const void* kpool, const void* vpool, int n_blocks, int bs,
+                                       const int* positions, const int* seq_of_row, const int* tables,
+                                       int table_stride, const int* tile_row0, const int* tile_nrows, int n_tiles,
+                                       int nh, int nkv, int d, float scale, int window, float softcap, int sink,
+                                       int* err, cudaStream_t stream) {
+  return cuca_attention_prefill_tc_sv(q, q_stride, n_rows_total, out, out_stride, kpool, vpool, n_blocks, bs, positions,
+                                      seq_of_row, tables, table_stride, tile_row0, tile_nrows, n_tiles, nh, nkv, d, scale,
+                                      window, softcap, sink, nullptr, err, stream);
 }

@@ -87,6 +87,53 @@ CUCA_API int cuca_embed(const void* table, int table_dtype, const int* tokens, f
   return cuca_embed_scaled(table, table_dtype, tokens, x, n_rows, E, V, 1.f, err, stream);
 }
 
+// ---------------------------------------------------------------- embedding followed by an RMS norm
+// x[r] = e / sqrt(mean(e^2) + eps) * w with e = table[tokens[r]] * scale: the stream starts as the normed embedding
+// row. One block per row, two passes over the row (the second one hits the cache); the sum's order depends on E alone.
+template <typename T>
+__global__ void __launch_bounds__(256)
+embed_norm_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x, int E, int V,
+                  float scale, const float* __restrict__ w, float eps, int* err) {
+  __shared__ float red[8];
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int tok = tokens[row];
+  float* dst = x + (size_t)row * E;
+  if (tok < 0 || tok >= V) {
+    if (threadIdx.x == 0 && err) atomicExch(err, CUCA_ERR_TOKEN_RANGE);
+    for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = 0.f;
+    return;
+  }
+  const T* src = table + (size_t)tok * E;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) { const float v = to_f32(src[i]) * scale; ss = fmaf(v, v, ss); }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float inv = 1.f / sqrtf(tot / (float)E + eps);
+  for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = to_f32(src[i]) * scale * inv * w[i];
+}
+
+CUCA_API int cuca_embed_norm(const void* table, int table_dtype, const int* tokens, float* x, int n_rows, int E, int V,
+                             float scale, const float* w, float eps, int* err, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CUCA_REQUIRE(E > 0 && V > 0 && w != nullptr, "embed_norm: bad sizes E=%d V=%d", E, V);
+  if (table_dtype == CUCA_F32)
+    cuca_launch(embed_norm_kernel<float>, dim3(n_rows), dim3(256), 0, stream, true, (const float*)table, tokens, x, E, V,
+                scale, w, eps, err);
+  else if (table_dtype == CUCA_BF16)
+    cuca_launch(embed_norm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, true, (const __nv_bfloat16*)table,
+                tokens, x, E, V, scale, w, eps, err);
+  else
+    CUCA_REQUIRE(false, "embed_norm: unknown dtype %d", table_dtype);
+  CUCA_CHECK_LAUNCH("embed_norm");
+  return 0;
+}
+
 // ---------------------------------------------------------------- RMSNorm
 // One block per output row. Every thread takes four consecutive values at a time and the block is as wide as
 // the row needs (up to 1024 threads), so all loads of a row are in flight together. The reduction order depends
@@ -474,6 +521,96 @@ CUCA_API int cuca_glu_capped(const void* gu, void* out, int dtype, int n_rows, i
   else
     CUCA_REQUIRE(false, "glu_capped: unknown dtype %d", dtype);
   CUCA_CHECK_LAUNCH("glu_capped");
+  return 0;
+}
+
+// ---------------------------------------------------------------- a gated unit with a chosen activation
+// out[r, j] = act(gu[r, j]) * gu[r, ff + j]; act 0: silu, 1: the tanh form of gelu,
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float glu_activation(float z, int act) {
+  if (act == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.f + expf(-z));
+}
+
+template <typename T>
+__global__ void glu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int ff, size_t total, int act) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / ff;
+    const int j = (int)(i % ff);
+    out[i] = from_f32<T>(glu_activation(to_f32(gu[r * 2 * ff + j]), act) * to_f32(gu[r * 2 * ff + ff + j]));
+  }
+}
+
+CUCA_API int cuca_glu_act(const void* gu, void* out, int dtype, int n_rows, int ff, int act, cudaStream_t stream) {
+  const size_t total = (size_t)n_rows * ff;
+  if (total == 0) return 0;
+  CUCA_REQUIRE(act == 0 || act == 1, "glu_act: unknown activation %d", act);
+  size_t blocks = (total + 255) / 256;
+  blocks = blocks > 16384 ? 16384 : blocks;
+  if (dtype == CUCA_F32)
+    cuca_launch(glu_act_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, true, (const float*)gu, (float*)out,
+                ff, total, act);
+  else if (dtype == CUCA_BF16)
+    cuca_launch(glu_act_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, true,
+                (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, ff, total, act);
+  else
+    CUCA_REQUIRE(false, "glu_act: unknown dtype %d", dtype);
+  CUCA_CHECK_LAUNCH("glu_act");
+  return 0;
+}
+
+// ---------------------------------------------------------------- one gate per head
+// a[r, h dv + j] *= sigmoid(gate[r, h]) for every head h of dv values; a: rows of stride lda, gate: rows of stride ldg.
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ a, int lda, const T* __restrict__ gate, int ldg, int n_rows, int H,
+                                 int dv) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t total = (size_t)n_rows * H * dv;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / ((size_t)H * dv);
+    const int c = (int)(i % ((size_t)H * dv));
+    const float g = to_f32(gate[r * ldg + c / dv]);
+    T* at = a + r * lda + c;
+    *at = from_f32<T>(to_f32(*at) / (1.f + expf(-g)));
+  }
+}
+
+CUCA_API int cuca_head_gate(void* a, int lda, const void* gate, int ldg, int dtype, int n_rows, int H, int dv,
+                            cudaStream_t stream) {
+  const size_t total = (size_t)n_rows * H * dv;
+  if (total == 0) return 0;
+  size_t blocks = (total + 255) / 256;
+  blocks = blocks > 16384 ? 16384 : blocks;
+  if (dtype == CUCA_F32)
+    cuca_launch(head_gate_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, true, (float*)a, lda,
+                (const float*)gate, ldg, n_rows, H, dv);
+  else if (dtype == CUCA_BF16)
+    cuca_launch(head_gate_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, true, (__nv_bfloat16*)a,
+                lda, (const __nv_bfloat16*)gate, ldg, n_rows, H, dv);
+  else
+    CUCA_REQUIRE(false, "head_gate: unknown dtype %d", dtype);
+  CUCA_CHECK_LAUNCH("head_gate");
+  return 0;
+}
+
+// ---------------------------------------------------------------- a smooth cap: a <- c tanh(a / c), 32-bit, in place
+__global__ void softcap_kernel(float* __restrict__ a, size_t n, float cap) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    a[i] = cap * tanhf(a[i] / cap);
+}
+
+CUCA_API int cuca_softcap(float* a, size_t n, float cap, cudaStream_t stream) {
+  if (n == 0) return 0;
+  CUCA_REQUIRE(cap > 0.f, "softcap: the cap %g must be positive", (double)cap);
+  size_t blocks = (n + 255) / 256;
+  blocks = blocks > 16384 ? 16384 : blocks;
+  cuca_launch(softcap_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, true, a, n, cap);
+  CUCA_CHECK_LAUNCH("softcap");
   return 0;
 }
 

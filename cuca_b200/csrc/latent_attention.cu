@@ -5,7 +5,7 @@
 //   out_h = V_h (sum_j p_j c_j),
 // so a head's query is carried into the latent space once per row (`head_linear` with U_h^T), every head attends
 // over the same cached rows, and the weighted sum of latents is taken out through V_h (`head_linear` again).
-//   latent_prepare    norms c, rotates k_rot and the heads' q_rot (adjacent pairs), writes the cache row
+//   latent_prepare    norms c, rotates k_rot and the heads' q_rot (pairs (2i, 2i + 1) or (i, i + n/2)), writes the cache row
 //   head_linear       out[t, h, :] = W_h a[t, h, :] for every head, optionally times sigmoid(gate)
 //   latent_attention  plain form: one warp per (row, head), keys in tiles of 32 absolute positions
 // Scores, softmax, norms and rotation are 32-bit; the cache has the compute dtype.
@@ -20,7 +20,8 @@ template <typename TC>
 __global__ void __launch_bounds__(256)
 latent_prepare_kernel(const float* __restrict__ qkg, int ld, int H, int dn, int dr, int rank,
                       const float* __restrict__ c_gain, float eps, const float* __restrict__ cos_t,
-                      const float* __restrict__ sin_t, int table_rows, int rot_dims, float* __restrict__ qk,
+                      const float* __restrict__ sin_t, int table_rows, int rot_dims, int half_pairs,
+                      float* __restrict__ qk,
                       TC* __restrict__ pool, int n_blocks, int bs, const int* __restrict__ positions,
                       const int* __restrict__ seq_of_row, const int* __restrict__ tables, int table_stride, int* err) {
   __shared__ float red[8];
@@ -39,17 +40,22 @@ latent_prepare_kernel(const float* __restrict__ qkg, int ld, int H, int dn, int 
   const float* sn = sin_t + (size_t)pos * half;
   const float* qrow = qkg + (size_t)row * ld;
   const int Dk = rank + dr;
+  // value j (< rot_dims) of a vector turned by the position: with its neighbour (2i, 2i + 1), or, half_pairs, with the
+  // value half the rotated size away (i, i + rot_dims / 2)
+  auto turned = [&](const float* src, int j) {
+    if (half_pairs) {
+      const bool up = j >= half;
+      const int pr = up ? j - half : j;
+      return up ? src[j] * cs[pr] + src[j - half] * sn[pr] : src[j] * cs[pr] - src[j + half] * sn[pr];
+    }
+    const int pr = j >> 1;
+    return (j & 1) ? src[j] * cs[pr] + src[j - 1] * sn[pr] : src[j] * cs[pr] - src[j + 1] * sn[pr];
+  };
   // the heads' rotated parts
   for (int i = threadIdx.x; i < H * dr; i += 256) {
     const int h = i / dr, j = i % dr;
     const float* src = qrow + (size_t)h * (dn + dr) + dn;
-    float v = src[j];
-    if (j < rot_dims) {
-      const int pr = j >> 1;
-      const float c = cs[pr], s = sn[pr];
-      v = (j & 1) ? src[j] * c + src[j - 1] * s : src[j] * c - src[j + 1] * s;
-    }
-    qk[((size_t)row * H + h) * Dk + rank + j] = v;
+    qk[((size_t)row * H + h) * Dk + rank + j] = j < rot_dims ? turned(src, j) : src[j];
   }
   // the cache row
   const float* dkv = qrow + (size_t)H * (dn + dr);
@@ -70,15 +76,7 @@ latent_prepare_kernel(const float* __restrict__ qkg, int ld, int H, int dn, int 
   TC* dst = pool + ((size_t)blk * bs + (pos % bs)) * Dk;
   for (int i = threadIdx.x; i < rank; i += 256) dst[i] = from_f32<TC>(dkv[i] * inv * c_gain[i]);
   const float* kr = dkv + rank;
-  for (int j = threadIdx.x; j < dr; j += 256) {
-    float v = kr[j];
-    if (j < rot_dims) {
-      const int pr = j >> 1;
-      const float c = cs[pr], s = sn[pr];
-      v = (j & 1) ? kr[j] * c + kr[j - 1] * s : kr[j] * c - kr[j + 1] * s;
-    }
-    dst[rank + j] = from_f32<TC>(v);
-  }
+  for (int j = threadIdx.x; j < dr; j += 256) dst[rank + j] = from_f32<TC>(j < rot_dims ? turned(kr, j) : kr[j]);
 }
 
 // out[t, h, n] = sum_k a[t, h, k] w[h, n, k]  (* sigmoid(gate[t, h N + n])). Tiles of 64 rows x 64 outputs, 256
@@ -270,7 +268,7 @@ __global__ void __launch_bounds__(128)
 latent_attention_kernel(const float* __restrict__ qk, float* __restrict__ out, const TC* __restrict__ pool,
                         int n_blocks, int bs, const int* __restrict__ positions, const int* __restrict__ seq_of_row,
                         const int* __restrict__ tables, int table_stride, int H, int rank, int Dk, float scale,
-                        int window, int* err) {
+                        int window, const float* __restrict__ sink, int* err) {
   extern __shared__ float qs[];  // [4][Dk]
   pdl_trigger();
   pdl_wait();
@@ -331,6 +329,13 @@ latent_attention_kernel(const float* __restrict__ qk, float* __restrict__ out, c
     }
     m = m_new;
   }
+  if (sink) {  // one more term exp(sink[head]) in the denominator, with no value
+    const float m_new = fmaxf(m, sink[head]);
+    const float corr = expf(m - m_new);
+    l = l * corr + expf(sink[head] - m_new);
+#pragma unroll
+    for (int c = 0; c < NACC; ++c) acc[c] *= corr;
+  }
   const float inv = l > 0.f ? 1.f / l : 0.f;
   float* o = out + ((size_t)row * H + head) * rank;
 #pragma unroll
@@ -344,24 +349,34 @@ latent_attention_kernel(const float* __restrict__ qk, float* __restrict__ out, c
 
 CUCA_API int cuca_latent_max_rank() { return 1024; }
 
-CUCA_API int cuca_latent_prepare(const float* qkg, int ld, int H, int dn, int dr, int rank, const float* c_gain,
-                                 float eps, const float* cos_t, const float* sin_t, int table_rows, int rot_dims,
-                                 float* qk, void* pool, int pool_dtype, int n_blocks, int bs, const int* positions,
-                                 const int* seq_of_row, const int* tables, int table_stride, int n_rows, int* err,
-                                 cudaStream_t stream) {
+// half_pairs 0: rotated values pair as (2i, 2i + 1); 1: as (i, i + rot_dims / 2).
+CUCA_API int cuca_latent_prepare_p(const float* qkg, int ld, int H, int dn, int dr, int rank, const float* c_gain,
+                                   float eps, const float* cos_t, const float* sin_t, int table_rows, int rot_dims,
+                                   int half_pairs, float* qk, void* pool, int pool_dtype, int n_blocks, int bs,
+                                   const int* positions, const int* seq_of_row, const int* tables, int table_stride,
+                                   int n_rows, int* err, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(H > 0 && dn >= 0 && dr >= 0 && rank > 0, "latent_prepare: bad sizes");
   CUCA_REQUIRE(rot_dims % 2 == 0 && rot_dims <= dr, "latent_prepare: %d rotated dimensions do not fit %d", rot_dims, dr);
 #define LP(TC)                                                                                                       \
   cuca_launch(latent_prepare_kernel<TC>, dim3(n_rows), dim3(256), 0, stream, true, qkg, ld, H, dn, dr, rank, c_gain, \
-              eps, cos_t, sin_t, table_rows, rot_dims, qk, (TC*)pool, n_blocks, bs, positions, seq_of_row, tables,   \
-              table_stride, err)
+              eps, cos_t, sin_t, table_rows, rot_dims, half_pairs, qk, (TC*)pool, n_blocks, bs, positions, seq_of_row, \
+              tables, table_stride, err)
   if (pool_dtype == CUCA_F32) LP(float);
   else if (pool_dtype == CUCA_BF16) LP(__nv_bfloat16);
   else CUCA_REQUIRE(false, "latent_prepare: unknown dtype %d", pool_dtype);
 #undef LP
   CUCA_CHECK_LAUNCH("latent_prepare");
   return 0;
+}
+
+CUCA_API int cuca_latent_prepare(const float* qkg, int ld, int H, int dn, int dr, int rank, const float* c_gain,
+                                 float eps, const float* cos_t, const float* sin_t, int table_rows, int rot_dims,
+                                 float* qk, void* pool, int pool_dtype, int n_blocks, int bs, const int* positions,
+                                 const int* seq_of_row, const int* tables, int table_stride, int n_rows, int* err,
+                                 cudaStream_t stream) {
+  return cuca_latent_prepare_p(qkg, ld, H, dn, dr, rank, c_gain, eps, cos_t, sin_t, table_rows, rot_dims, 0, qk, pool,
+                               pool_dtype, n_blocks, bs, positions, seq_of_row, tables, table_stride, n_rows, err, stream);
 }
 
 // a: 32-bit, element (t, h, k) at a[t * lda + h * a_head + k]; w: [H, N, K]; out element (t, h, n) at
@@ -410,10 +425,12 @@ CUCA_API int cuca_head_linear(const float* a, int lda, int a_head, const void* w
   return 0;
 }
 
-CUCA_API int cuca_latent_attention(const float* qk, float* out, const void* pool, int pool_dtype, int n_blocks, int bs,
-                                   const int* positions, const int* seq_of_row, const int* tables, int table_stride,
-                                   int n_rows, int H, int rank, int Dk, float scale, int window, int* err,
-                                   cudaStream_t stream) {
+// sink (or null): 32-bit, one number per head: the softmax's denominator holds one more term exp(sink[head]) that has
+// no value and is not scaled.
+CUCA_API int cuca_latent_attention_s(const float* qk, float* out, const void* pool, int pool_dtype, int n_blocks, int bs,
+                                     const int* positions, const int* seq_of_row, const int* tables, int table_stride,
+                                     int n_rows, int H, int rank, int Dk, float scale, int window, const float* sink,
+                                     int* err, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(rank > 0 && rank <= Dk && rank <= cuca_latent_max_rank(), "latent_attention: latent size %d is outside 1..%d",
                rank, cuca_latent_max_rank());
@@ -422,7 +439,7 @@ CUCA_API int cuca_latent_attention(const float* qk, float* out, const void* pool
   const size_t smem = (size_t)4 * Dk * sizeof(float);
 #define LA(TC, NACC)                                                                                              \
   cuca_launch(latent_attention_kernel<TC, NACC>, grid, dim3(128), smem, stream, true, qk, out, (const TC*)pool,   \
-              n_blocks, bs, positions, seq_of_row, tables, table_stride, H, rank, Dk, scale, window, err)
+              n_blocks, bs, positions, seq_of_row, tables, table_stride, H, rank, Dk, scale, window, sink, err)
 #define LA_BY_RANK(TC)                    \
   do {                                    \
     if (rank <= 128) LA(TC, 4);           \
@@ -437,4 +454,12 @@ CUCA_API int cuca_latent_attention(const float* qk, float* out, const void* pool
 #undef LA
   CUCA_CHECK_LAUNCH("latent_attention");
   return 0;
+}
+
+CUCA_API int cuca_latent_attention(const float* qk, float* out, const void* pool, int pool_dtype, int n_blocks, int bs,
+                                   const int* positions, const int* seq_of_row, const int* tables, int table_stride,
+                                   int n_rows, int H, int rank, int Dk, float scale, int window, int* err,
+                                   cudaStream_t stream) {
+  return cuca_latent_attention_s(qk, out, pool, pool_dtype, n_blocks, bs, positions, seq_of_row, tables, table_stride,
+                                 n_rows, H, rank, Dk, scale, window, nullptr, err, stream);
 }

@@ -62,6 +62,7 @@ struct Params {
   int H, rank, Dk;
   float scale_log2;       // scale * log2(e)
   int window;
+  const float* sink;      // (or null) per head: one more term exp(sink[head]) without a value in the denominator
   int TQ, HB;             // tokens x heads of a group, TQ * HB = 16
   int* err;
   // Single tokens with few groups: the key tiles of a group are dealt to n_splits CTAs (blockIdx.z), each leaves its
@@ -296,9 +297,10 @@ latent_attention_mma_kernel(Params p) {
   for (int i = 0; i < 2; ++i) {
     if (!rvalid[i]) continue;
     const int r = g + 8 * i;
-    const float L = wsum[r] + wsum[16 + r] + wsum[32 + r] + wsum[48 + r];
-    const float inv = L > 0.f ? 1.f / L : 0.f;
+    float L = wsum[r] + wsum[16 + r] + wsum[32 + r] + wsum[48 + r];
     const int tok = r / p.HB, head = head0 + r % p.HB;
+    if (p.sink && m[i] != -INFINITY) L += exp2f(p.sink[head] * 1.4426950408889634f - m[i]);  // (m in log2 units)
+    const float inv = L > 0.f ? 1.f / L : 0.f;
     float* o = p.out + ((size_t)(row0 + tok) * H + head) * rank + warp * DW;
 #pragma unroll
     for (int n = 0; n < NT8; ++n) {
@@ -314,7 +316,8 @@ latent_attention_mma_kernel(Params p) {
 // (up to 64 splits).
 __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                     float* __restrict__ out, const int* __restrict__ rows,
-                                    const int* __restrict__ seq_of_row, int n_splits, int H, int rank) {
+                                    const int* __restrict__ seq_of_row, int n_splits, int H, int rank,
+                                    const float* __restrict__ sink) {
   pdl_trigger();
   pdl_wait();
   const int grp = blockIdx.x, hb = blockIdx.y, r = blockIdx.z;
@@ -341,6 +344,7 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const fl
       L += lz[k] * e[k];
     }
     L = warp_sum(L);
+    if (sink && M != -INFINITY) L += exp2f(sink[head] * 1.4426950408889634f - M);
     const float inv = L > 0.f ? 1.f / L : 0.f;
     wz[threadIdx.x] = e[0] * inv;
     wz[threadIdx.x + 32] = e[1] * inv;
@@ -384,11 +388,13 @@ CUCA_API int cuca_latent_attention_mma_supported(int rank, int Dk) {
 
 // Groups of rows: with tile_row0/tile_nrows, `n_groups` runs of up to 16 consecutive rows of one request (one head
 // per CTA); without, `n_groups` single rows (`rows`, or 0..n_groups-1 when null) with 16 heads per CTA.
-CUCA_API int cuca_latent_attention_mma(const float* qk, float* out, const void* pool, int n_blocks, int bs,
-                                       const int* positions, const int* seq_of_row, const int* tables,
-                                       int table_stride, const int* tile_row0, const int* tile_nrows, const int* rows,
-                                       int n_groups, int H, int rank, int Dk, float scale, int window, int n_splits,
-                                       float* part_acc, float* part_ml, int* err, cudaStream_t stream) {
+// sink (or null): 32-bit, one number per head: one more term exp(sink[head]) without a value in every denominator.
+CUCA_API int cuca_latent_attention_mma_s(const float* qk, float* out, const void* pool, int n_blocks, int bs,
+                                         const int* positions, const int* seq_of_row, const int* tables,
+                                         int table_stride, const int* tile_row0, const int* tile_nrows, const int* rows,
+                                         int n_groups, int H, int rank, int Dk, float scale, int window,
+                                         const float* sink, int n_splits, float* part_acc, float* part_ml, int* err,
+                                         cudaStream_t stream) {
   if (n_groups == 0) return 0;
   CUCA_REQUIRE(cuca_latent_attention_mma_supported(rank, Dk), "latent_attention_mma: sizes rank=%d Dk=%d are not taken",
                rank, Dk);
@@ -396,7 +402,7 @@ CUCA_API int cuca_latent_attention_mma(const float* qk, float* out, const void* 
   p.qk = qk; p.out = out; p.pool = (const bf16*)pool; p.n_blocks = n_blocks; p.bs = bs; p.positions = positions;
   p.seq_of_row = seq_of_row; p.tables = tables; p.table_stride = table_stride; p.tile_row0 = tile_row0;
   p.tile_nrows = tile_nrows; p.rows = rows; p.H = H; p.rank = rank; p.Dk = Dk;
-  p.scale_log2 = scale * 1.4426950408889634f; p.window = window; p.err = err;
+  p.scale_log2 = scale * 1.4426950408889634f; p.window = window; p.err = err; p.sink = sink;
   p.n_splits = (tile_row0 == nullptr && n_splits > 1 && part_acc && part_ml) ? n_splits : 1;
   p.part_acc = part_acc; p.part_ml = part_ml;
   CUCA_REQUIRE(p.n_splits <= 64, "latent_attention_mma: %d splits exceed 64", n_splits);
@@ -414,8 +420,18 @@ CUCA_API int cuca_latent_attention_mma(const float* qk, float* out, const void* 
   CUCA_CHECK_LAUNCH("latent_attention_mma");
   if (p.n_splits > 1) {
     cuca_launch(latent_merge_kernel, dim3(n_groups, head_blocks, 16), dim3(128), 0, stream, true,
-                (const float*)part_acc, (const float*)part_ml, out, rows, seq_of_row, p.n_splits, H, rank);
+                (const float*)part_acc, (const float*)part_ml, out, rows, seq_of_row, p.n_splits, H, rank, sink);
     CUCA_CHECK_LAUNCH("latent_merge");
   }
   return 0;
+}
+
+CUCA_API int cuca_latent_attention_mma(const float* qk, float* out, const void* pool, int n_blocks, int bs,
+                                       const int* positions, const int* seq_of_row, const int* tables,
+                                       int table_stride, const int* tile_row0, const int* tile_nrows, const int* rows,
+                                       int n_groups, int H, int rank, int Dk, float scale, int window, int n_splits,
+                                       float* part_acc, float* part_ml, int* err, cudaStream_t stream) {
+  return cuca_latent_attention_mma_s(qk, out, pool, n_blocks, bs, positions, seq_of_row, tables, table_stride, tile_row0,
+                                     tile_nrows, rows, n_groups, H, rank, Dk, scale, window, nullptr, n_splits, part_acc,
+                                     part_ml, err, stream);
 }

@@ -6,7 +6,9 @@
 //                     o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)
 //   forget_scan     linear attention whose forget gate f (per key channel) is also one minus its write strength:
 //                     S <- f * S (rows) + (1 - f) v^T;  o = S^T q
-//   head_norm_gate  out = o / rms(o) per head, times a weight, times sigmoid(gate)
+//   retention_scan  linear attention with one fixed decay per head and no denominator:
+//                     S <- decay S + k v^T;  o = S^T q
+//   head_norm_gate  out = o / rms(o) per head, times a weight (or none), times sigmoid(gate) or silu(gate)
 // What does not depend on the state (unit vectors, decays, gates) is computed for all rows at once by a preparing
 // kernel, in place. A scan block then takes one (head, request, run of value columns) and walks the request's rows of
 // the step in order from the state its slot holds, leaving the new state there. A value column's state rows live in
@@ -209,12 +211,49 @@ __global__ void forget_prepare_kernel(float* __restrict__ proj, int ld, int q_co
   }
 }
 
+// Per row, in place, of a 32-bit projection [q | k | ...] (H heads of d each): the first `rot` values of every q and k
+// head turn by the row's position in pairs (i, i + rot/2) with the angle tables' row of that position; k is then
+// multiplied by k_scale. One thread per (row, head, pair or unrotated value).
+__global__ void retention_prepare_kernel(float* __restrict__ proj, int ld, int q_col, int k_col,
+                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                         int table_rows, int rot, float k_scale, const int* __restrict__ positions,
+                                         const int* __restrict__ seq_of_row, int n_rows, int H, int d, int* err) {
+  pdl_trigger();
+  pdl_wait();
+  const int half = rot / 2, per_head = half + (d - rot);
+  const size_t per_row = (size_t)2 * H * per_head;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < (size_t)n_rows * per_row;
+       e += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = e / per_row;
+    const int w = (int)(e % per_row);
+    if (seq_of_row[row] < 0) continue;
+    const int which = w / (H * per_head), hh = (w / per_head) % H, i = w % per_head;
+    float* head = proj + row * ld + (which ? k_col : q_col) + (size_t)hh * d;
+    const float mul = which ? k_scale : 1.f;
+    if (i < half) {
+      const int pos = positions[row];
+      if (pos < 0 || pos >= table_rows) {
+        if (err) atomicExch(err, CUCA_ERR_TOKEN_RANGE);
+        continue;
+      }
+      const float c = cos_t[(size_t)pos * half + i], sn = sin_t[(size_t)pos * half + i];
+      const float a = head[i], b = head[i + half];
+      head[i] = (a * c - b * sn) * mul;
+      head[i + half] = (b * c + a * sn) * mul;
+    } else if (which) {
+      head[rot + (i - half)] *= mul;
+    }
+  }
+}
+
 // proj: 32-bit rows of stride ld, prepared: q heads at q_col (H heads of d), forget gates at f_col (H heads of d),
 // v heads at v_col (H heads of dv). state: [slots, H, dv, d]. out: [rows, H dv]. The delta scan's sibling without a
 // correction: one shuffled sum per token and column.
-template <int NR>
+// RET (retention): the second staged vector is the key k instead of the gate, and the state decays by one number per
+// head: S <- decay[h] S + k v^T.
+template <int NR, bool RET>
 __global__ void forget_scan_kernel(const float* __restrict__ proj, int ld, int q_col, int f_col, int v_col,
-                                   float* __restrict__ state, float* __restrict__ out,
+                                   const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ out,
                                    const int* __restrict__ req_row0, const int* __restrict__ req_count,
                                    const int* __restrict__ slots, int H, int d, int dv, int NS, int PB, int TC, int wide) {
   extern __shared__ __align__(16) float sm[];
@@ -238,7 +277,7 @@ __global__ void forget_scan_kernel(const float* __restrict__ proj, int ld, int q
     for (int e = threadIdx.x; e < 2 * TC * fill; e += blockDim.x) {
       const int t = e / fill, w = e % fill;
       float* tok = sm + (size_t)t * per;
-      if (w < 2 * spare) tok[(w / spare) * dpp + staged_at<NR>(d + w % spare)] = w / spare == 1 ? 1.f : 0.f;
+      if (w < 2 * spare) tok[(w / spare) * dpp + staged_at<NR>(d + w % spare)] = (w / spare == 1 && !RET) ? 1.f : 0.f;
       else tok[2 * dpp + (w - 2 * spare)] = 0.f;
     }
   }
@@ -262,6 +301,7 @@ __global__ void forget_scan_kernel(const float* __restrict__ proj, int ld, int q
   };
   const int cv = col_local < PB ? col_local : PB - 1;
   const int n_chunks = (n + TC - 1) / TC;
+  const float dec = RET ? decay[h] : 0.f;
   stage(0, 0);
   for (int c = 0; c < n_chunks; ++c) {
     if (c + 1 < n_chunks) { stage((c + 1) * TC, (c + 1) & 1); cp_async_wait<1>(); }
@@ -282,9 +322,14 @@ __global__ void forget_scan_kernel(const float* __restrict__ proj, int ld, int q
 #pragma unroll
       for (int i = 0; i < NR / 4; ++i) {
         const float4 f4 = gf[i], qv = gq[i];
+        if (RET) {  // decay S + k v
+          S[4 * i] = fmaf(dec, S[4 * i], f4.x * v); S[4 * i + 1] = fmaf(dec, S[4 * i + 1], f4.y * v);
+          S[4 * i + 2] = fmaf(dec, S[4 * i + 2], f4.z * v); S[4 * i + 3] = fmaf(dec, S[4 * i + 3], f4.w * v);
+        } else {
         // f S + (1 - f) v, each product rounded as the plain recurrence rounds it
         S[4 * i] = fmaf(f4.x, S[4 * i], (1.f - f4.x) * v); S[4 * i + 1] = fmaf(f4.y, S[4 * i + 1], (1.f - f4.y) * v);
         S[4 * i + 2] = fmaf(f4.z, S[4 * i + 2], (1.f - f4.z) * v); S[4 * i + 3] = fmaf(f4.w, S[4 * i + 3], (1.f - f4.w) * v);
+        }
         p0 = fmaf(S[4 * i], qv.x, p0); p1 = fmaf(S[4 * i + 1], qv.y, p1);
         p2 = fmaf(S[4 * i + 2], qv.z, p2); p3 = fmaf(S[4 * i + 3], qv.w, p3);
       }
@@ -468,8 +513,9 @@ __global__ void mlstm_commit_kernel(const float* __restrict__ nm_new, float* __r
 }
 
 // o: [rows, H dv] 32-bit. out[r, h, j] = o / sqrt(mean_j o^2 + eps) * w[h * w_head + j] * sigmoid(gate[r, h dv + j]);
-// w_head 0: one weight vector for every head. gate: rows of stride ld_g (TG), null for none.
-template <typename TG, typename TO>
+// w_head 0: one weight vector for every head; w null: no weight. gate: rows of stride ld_g (TG), null for none;
+// SILU: the gate's factor is silu(gate) instead of sigmoid(gate).
+template <typename TG, typename TO, bool SILU>
 __global__ void __launch_bounds__(256)
 head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, int w_head,
                       const TG* __restrict__ gate, int ld_g, TO* __restrict__ out, int H, int dv, float eps,
@@ -483,7 +529,8 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, 
   const size_t row = (size_t)(item / H);
   const int h = (int)(item % H);
   const float* orow = o + (size_t)item * dv;
-  const float* wh = w + (size_t)h * w_head;
+  const float* wh = w ? w + (size_t)h * w_head : nullptr;
+  auto gate_of = [](float g) { return SILU ? g * sigmoidf_(g) : sigmoidf_(g); };
   const TG* grow = gate ? gate + row * ld_g + (size_t)h * dv : nullptr;
   TO* dst = out + (size_t)item * dv;
   if ((dv & 3) == 0) {
@@ -495,10 +542,14 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, 
     const float inv = 1.f / sqrtf(warp_sum(ss) / (float)dv + eps);
     for (int j = lane * 4; j < dv; j += 128) {
       const float4 v = *reinterpret_cast<const float4*>(orow + j);
-      float r[4] = {v.x * inv * wh[j], v.y * inv * wh[j + 1], v.z * inv * wh[j + 2], v.w * inv * wh[j + 3]};
+      float r[4] = {v.x * inv, v.y * inv, v.z * inv, v.w * inv};
+      if (wh) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) r[e] *= wh[j + e];
+      }
       if (grow) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) r[e] *= sigmoidf_(to_f32(grow[j + e]));
+        for (int e = 0; e < 4; ++e) r[e] *= gate_of(to_f32(grow[j + e]));
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) dst[j + e] = from_f32<TO>(r[e]);
@@ -509,8 +560,8 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, 
   for (int j = lane; j < dv; j += 32) ss = fmaf(orow[j], orow[j], ss);
   const float inv = 1.f / sqrtf(warp_sum(ss) / (float)dv + eps);
   for (int j = lane; j < dv; j += 32) {
-    float v = orow[j] * inv * wh[j];
-    if (grow) v *= sigmoidf_(to_f32(grow[j]));
+    float v = orow[j] * inv * (wh ? wh[j] : 1.f);
+    if (grow) v *= gate_of(to_f32(grow[j]));
     dst[j] = from_f32<TO>(v);
   }
 }
@@ -655,8 +706,8 @@ CUCA_API int cuca_forget_scan(float* proj, int ld, int q_col, int f_col, int v_c
   const int wide = d % 4 == 0 && ld % 4 == 0 && q_col % 4 == 0 && f_col % 4 == 0 && ((uintptr_t)proj & 15) == 0;
   dim3 grid(H, n_seqs, (dv + pb - 1) / pb);
 #define FS(NR)                                                                                                     \
-  cuca_launch(forget_scan_kernel<NR>, grid, dim3(threads), smem, stream, true, (const float*)proj, ld, q_col, f_col, \
-              v_col, state, out, req_row0, req_count, slots, H, d, dv, ns, pb, tc, wide)
+  cuca_launch(forget_scan_kernel<NR, false>, grid, dim3(threads), smem, stream, true, (const float*)proj, ld, q_col, \
+              f_col, v_col, (const float*)nullptr, state, out, req_row0, req_count, slots, H, d, dv, ns, pb, tc, wide)
   if (nr == 4) FS(4);
   else if (nr == 8) FS(8);
   else if (nr == 16) FS(16);
@@ -666,14 +717,67 @@ CUCA_API int cuca_forget_scan(float* proj, int ld, int q_col, int f_col, int v_c
   return 0;
 }
 
-CUCA_API int cuca_head_norm_gate(const float* o, const float* w, int w_head, const void* gate, int gate_dtype, int ld_g,
-                                 void* out, int out_dtype, int n_rows, int H, int dv, float eps, cudaStream_t stream) {
+// Retention along every request's rows. proj: 32-bit rows of stride ld holding q heads at q_col, k heads at k_col (H
+// heads of d each) and v heads at v_col (H heads of dv). The preparing kernel turns the first `rot` values of every q
+// and k head by the row's position (pairs (i, i + rot/2); cos_t/sin_t: [table_rows, rot/2]) and multiplies k by
+// k_scale, in place; the scan then runs S <- decay[h] S + k v^T, o = S^T q from the state in the request's slot
+// (state: [slots, H, dv, d], out: [rows, H dv], both 32-bit).
+CUCA_API int cuca_retention_scan(float* proj, int ld, int q_col, int k_col, int v_col, const float* decay,
+                                 const float* cos_t, const float* sin_t, int table_rows, int rot, float k_scale,
+                                 const int* positions, float* state, float* out, const int* seq_of_row,
+                                 const int* req_row0, const int* req_count, const int* slots, int n_rows, int n_seqs,
+                                 int H, int d, int dv, int* err, cudaStream_t stream) {
+  if (n_seqs == 0 || n_rows == 0) return 0;
+  CUCA_REQUIRE(H > 0 && d > 0 && dv > 0, "retention_scan: bad sizes heads=%d dim=%d vdim=%d", H, d, dv);
+  CUCA_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "retention_scan: rotary size %d does not fit head size %d", rot, d);
+  CUCA_REQUIRE(n_seqs <= 65535, "retention_scan: %d requests exceed the launch limit", n_seqs);
+  int ns, nr;
+  CUCA_REQUIRE(split_rows(d, (long long)n_seqs * H * dv, &ns, &nr), "retention_scan: %d key channels exceed %d", d, 32 * MAXR);
+  {
+    size_t blocks = ((size_t)n_rows * 2 * H * (d - rot / 2) + 255) / 256;
+    blocks = blocks > 8192 ? 8192 : blocks;
+    cuca_launch(retention_prepare_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, true, proj, ld, q_col, k_col,
+                cos_t, sin_t, table_rows, rot, k_scale, positions, seq_of_row, n_rows, H, d, err);
+    CUCA_CHECK_LAUNCH("retention_prepare");
+  }
+  int pb = block_threads(ns, nr) / ns;
+  pb = pb > dv ? dv : pb;
+  const int threads = (pb * ns + 31) / 32 * 32;
+  const int per = (2 * ns * (nr == 4 ? 4 : nr + 4) + pb + 3) & ~3;
+  int tc = 46000 / (2 * per * 4);
+  tc = tc > 16 ? 16 : tc;
+  CUCA_REQUIRE(tc >= 1, "retention_scan: a token of %d key channels does not fit shared memory", d);
+  const size_t smem = (size_t)2 * tc * per * 4;
+  const int wide = d % 4 == 0 && ld % 4 == 0 && q_col % 4 == 0 && k_col % 4 == 0 && ((uintptr_t)proj & 15) == 0;
+  dim3 grid(H, n_seqs, (dv + pb - 1) / pb);
+#define RS(NR)                                                                                                     \
+  cuca_launch(forget_scan_kernel<NR, true>, grid, dim3(threads), smem, stream, true, (const float*)proj, ld, q_col,  \
+              k_col, v_col, decay, state, out, req_row0, req_count, slots, H, d, dv, ns, pb, tc, wide)
+  if (nr == 4) RS(4);
+  else if (nr == 8) RS(8);
+  else if (nr == 16) RS(16);
+  else RS(32);
+#undef RS
+  CUCA_CHECK_LAUNCH("retention_scan");
+  return 0;
+}
+
+// gate_act 0: the gate's factor is sigmoid(gate); 1: silu(gate). w null: no weight.
+CUCA_API int cuca_head_norm_gate_act(const float* o, const float* w, int w_head, const void* gate, int gate_dtype,
+                                     int ld_g, int gate_act, void* out, int out_dtype, int n_rows, int H, int dv,
+                                     float eps, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   const long long n_items = (long long)n_rows * H;
   dim3 grid((unsigned)((n_items + 7) / 8));
-#define HNG(TG, TO)                                                                                              \
-  cuca_launch(head_norm_gate_kernel<TG, TO>, grid, dim3(256), 0, stream, true, o, w, w_head, (const TG*)gate, ld_g, \
-              (TO*)out, H, dv, eps, n_items)
+#define HNG(TG, TO)                                                                                                 \
+  do {                                                                                                              \
+    if (gate_act)                                                                                                   \
+      cuca_launch(head_norm_gate_kernel<TG, TO, true>, grid, dim3(256), 0, stream, true, o, w, w_head,              \
+                  (const TG*)gate, ld_g, (TO*)out, H, dv, eps, n_items);                                            \
+    else                                                                                                            \
+      cuca_launch(head_norm_gate_kernel<TG, TO, false>, grid, dim3(256), 0, stream, true, o, w, w_head,             \
+                  (const TG*)gate, ld_g, (TO*)out, H, dv, eps, n_items);                                            \
+  } while (0)
   if (gate_dtype == CUCA_F32 && out_dtype == CUCA_F32) HNG(float, float);
   else if (gate_dtype == CUCA_F32 && out_dtype == CUCA_BF16) HNG(float, __nv_bfloat16);
   else if (gate_dtype == CUCA_BF16 && out_dtype == CUCA_BF16) HNG(__nv_bfloat16, __nv_bfloat16);
@@ -681,4 +785,9 @@ CUCA_API int cuca_head_norm_gate(const float* o, const float* w, int w_head, con
 #undef HNG
   CUCA_CHECK_LAUNCH("head_norm_gate");
   return 0;
+}
+
+CUCA_API int cuca_head_norm_gate(const float* o, const float* w, int w_head, const void* gate, int gate_dtype, int ld_g,
+                                 void* out, int out_dtype, int n_rows, int H, int dv, float eps, cudaStream_t stream) {
+  return cuca_head_norm_gate_act(o, w, w_head, gate, gate_dtype, ld_g, 0, out, out_dtype, n_rows, H, dv, eps, stream);
 }

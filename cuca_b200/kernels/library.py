@@ -121,6 +121,28 @@ _SIGNATURES = {
                              _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "cuca_forget_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "cuca_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, c_size_t, _P, _I, _I, _P, _P],
+    "cuca_embed_norm": [_P, _I, _P, _P, _I, _I, _I, _F, _P, _F, _P, _P],
+    "cuca_glu_act": [_P, _P, _I, _I, _I, _I, _P],
+    "cuca_head_gate": [_P, _I, _P, _I, _I, _I, _I, _I, _P],
+    "cuca_softcap": [_P, c_size_t, _F, _P],
+    "cuca_attention_generic_sv": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _F, _I,
+                                  _P, _P, _P],
+    "cuca_attention_decode_sv": [_P, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _F, _I, _P,
+                                 _I, _I, _P, _P, _P, _P],
+    "cuca_attention_prefill_sv": [_P, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _F, _I,
+                                  _P, _P, _P],
+    "cuca_attention_prefill_tc_sv": [_P, _I, _I, _P, _I, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I,
+                                     _F, _I, _P, _P, _P],
+    "cuca_norm_rope_store_w": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _F, _P, _P,
+                               _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "cuca_latent_prepare_p": [_P, _I, _I, _I, _I, _I, _P, _F, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I,
+                              _I, _P, _P],
+    "cuca_latent_attention_s": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P],
+    "cuca_latent_attention_mma_s": [_P, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _I, _P,
+                                    _P, _P, _P],
+    "cuca_retention_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _I, _I, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
+                            _P, _P],
+    "cuca_head_norm_gate_act": [_P, _P, _I, _P, _I, _I, _I, _P, _I, _I, _I, _I, _F, _P],
 }
 
 _lock = threading.Lock()

@@ -56,6 +56,15 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err: tor
                                         float(scale), _p(err), _stream()), "embed")
 
 
+def embed_norm(table, tokens, out, weight, eps: float, err, scale: float = 1.0) -> None:
+    """out[r] = e / sqrt(mean(e^2) + eps) * weight with e = table[tokens[r]] * scale, into the 32-bit stream."""
+    _cuda(table, tokens, out, weight)
+    V, E = table.shape
+    library.check(library.load().cuca_embed_norm(_p(table), dtype_code(table.dtype), _p(tokens), _p(out), tokens.shape[0],
+                                                 E, V, float(scale), _p(weight), float(eps), _p(err), _stream()),
+                  "embed_norm")
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, rows=None, groups: int = 1) -> None:
     """out = x / sqrt(mean(x^2) + eps) * weight per row; `groups` > 1: every one of that many equal consecutive parts
     of a row is divided by its own root mean square."""
@@ -102,6 +111,31 @@ def glu_capped(gate_up, out, limit: float, alpha: float) -> None:
     _cuda(gate_up, out)
     library.check(library.load().cuca_glu_capped(_p(gate_up), _p(out), dtype_code(out.dtype), out.shape[0], out.shape[1],
                                                  float(limit), float(alpha), _stream()), "glu_capped")
+
+
+GLU_SILU, GLU_GELU_TANH = 0, 1
+
+
+def glu_act(gate_up, out, act: int) -> None:
+    """out[r, j] = act(gate_up[r, j]) * gate_up[r, ff + j]; act: GLU_SILU or GLU_GELU_TANH."""
+    _cuda(gate_up, out)
+    library.check(library.load().cuca_glu_act(_p(gate_up), _p(out), dtype_code(out.dtype), out.shape[0], out.shape[1],
+                                              int(act), _stream()), "glu_act")
+
+
+def head_gate_(a, gate, n_heads: int, v_head_dim: int) -> None:
+    """a[r, h * dv + j] *= sigmoid(gate[r, h]): one gate per head; both of one dtype, rows of any stride."""
+    _cuda(a, gate)
+    library.check(library.load().cuca_head_gate(_p(a), a.stride(0), _p(gate), gate.stride(0), dtype_code(a.dtype),
+                                                a.shape[0], int(n_heads), int(v_head_dim), _stream()), "head_gate")
+
+
+def softcap_(a, cap: float) -> None:
+    """a <- cap tanh(a / cap) in place (32-bit)."""
+    _cuda(a)
+    if a.dtype != torch.float32 or not a.is_contiguous():
+        raise library.KernelError("softcap_ takes a contiguous 32-bit tensor")
+    library.check(library.load().cuca_softcap(_p(a), a.numel(), float(cap), _stream()), "softcap")
 
 
 def add_to_stream(x, delta) -> None:
@@ -395,16 +429,27 @@ def _decode_scratch(device, n_rows, n_heads, n_kv_heads, head_dim, n_splits):
 
 def attention_decode(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, rows, n_rows, n_heads,
                      n_kv_heads, head_dim, scale, window, chunk, n_splits, err, softcap: float = 0.0,
-                     sink: bool = False) -> None:
+                     sink: bool = False, sink_values=None) -> None:
     """The split-key decode form. `softcap` c > 0: a scaled score s becomes c tanh(s / c); `sink`: every row's
-    denominator holds one more exp(0) that has no value."""
+    denominator holds one more exp(0) that has no value, or exp(sink_values[head]) (32-bit, one number per query
+    head) when those are given."""
     lib = library.load()
     part, cnt = _decode_scratch(out.device, n_rows, n_heads, n_kv_heads, head_dim, n_splits)
-    library.check(lib.cuca_attention_decode_s(
+    library.check(lib.cuca_attention_decode_sv(
         _p(q), int(q_stride), _p(out), out.stride(0), _p(kpool), _p(vpool), kpool.shape[0], kpool.shape[2],
         _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(rows), n_rows, n_heads, n_kv_heads, head_dim,
-        float(scale), int(window or 0), float(softcap or 0.0), int(bool(sink)), chunk, n_splits, _p(part), _p(cnt),
-        _p(err), _stream()), "attention_decode")
+        float(scale), int(window or 0), float(softcap or 0.0), int(bool(sink)), _sink_values(sink_values, n_heads), chunk,
+        n_splits, _p(part), _p(cnt), _p(err), _stream()), "attention_decode")
+
+
+def _sink_values(sink_values, n_heads: int):
+    """The pointer of a sink's per-head scores (None: the sink's score is 0), checked for what the kernels assume."""
+    if sink_values is None:
+        return None
+    if sink_values.dtype != torch.float32 or sink_values.numel() != n_heads or not sink_values.is_contiguous():
+        raise library.KernelError(f"a sink's scores are {n_heads} contiguous 32-bit numbers, one per query head")
+    _cuda(sink_values)
+    return sink_values.data_ptr()
 
 
 def attention_decode_fused(partial, bias, cos, sin, rotary_dim, has_kv, out, kpool, vpool, positions, seq_of_row, tables,
@@ -431,13 +476,14 @@ def attention_decode_fused_supported(plan, cache, out_dtype, n_rows, n_heads, n_
 
 
 def attention_prefill(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, tile_row0, tile_nrows, n_tiles,
-                      n_heads, n_kv_heads, head_dim, scale, window, err, softcap: float = 0.0, sink: bool = False) -> None:
+                      n_heads, n_kv_heads, head_dim, scale, window, err, softcap: float = 0.0, sink: bool = False,
+                      sink_values=None) -> None:
     lib = library.load()
-    library.check(lib.cuca_attention_prefill_s(
+    library.check(lib.cuca_attention_prefill_sv(
         _p(q), int(q_stride), _p(out), out.stride(0), _p(kpool), _p(vpool), kpool.shape[0], kpool.shape[2],
         _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(tile_row0), _p(tile_nrows), n_tiles, n_heads,
-        n_kv_heads, head_dim, float(scale), int(window or 0), float(softcap or 0.0), int(bool(sink)), _p(err),
-        _stream()), "attention_prefill")
+        n_kv_heads, head_dim, float(scale), int(window or 0), float(softcap or 0.0), int(bool(sink)),
+        _sink_values(sink_values, n_heads), _p(err), _stream()), "attention_prefill")
 
 
 def attention_tc_supported(q, out, kpool, vpool, n_heads, n_kv_heads, head_dim) -> bool:
@@ -460,23 +506,23 @@ def attention_pair_tiles_mode(mode: int) -> None:
 
 def attention_prefill_tc(q, out, kpool, vpool, positions, seq_of_row, tables, tile_row0, tile_nrows, n_tiles,
                          n_heads, n_kv_heads, head_dim, scale, window, err, softcap: float = 0.0,
-                         sink: bool = False) -> None:
+                         sink: bool = False, sink_values=None) -> None:
     """Prefill attention on tcgen05; tiles of up to 128 consecutive rows of one request."""
     lib = library.load()
-    library.check(lib.cuca_attention_prefill_tc(
+    library.check(lib.cuca_attention_prefill_tc_sv(
         _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(kpool), _p(vpool), kpool.shape[0], kpool.shape[2],
         _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(tile_row0), _p(tile_nrows), n_tiles, n_heads,
-        n_kv_heads, head_dim, float(scale), int(window or 0), float(softcap or 0.0), int(bool(sink)), _p(err),
-        _stream()), "attention_prefill_tc")
+        n_kv_heads, head_dim, float(scale), int(window or 0), float(softcap or 0.0), int(bool(sink)),
+        _sink_values(sink_values, n_heads), _p(err), _stream()), "attention_prefill_tc")
 
 
 def attention(qkv, out, cache, step, plan, n_heads, n_kv_heads, head_dim, scale, window, err, softcap: float = 0.0,
-              sink: bool = False) -> None:
+              sink: bool = False, sink_values=None) -> None:
     """Paged causal attention of every row of the step; q is the head of each `qkv` row. bfloat16 with head
     sizes 16..128 in steps of 16 runs on tensor cores: single-token requests through the split-key decode form,
     portions of prompts through the prefill form; everything else (the 32-bit path, other head sizes) through
     the plain kernel. `softcap` c > 0: a scaled score s becomes c tanh(s / c); `sink`: one more exp(0) without a
-    value in every row's denominator."""
+    value in every row's denominator, or exp(sink_values[head]) when those (32-bit, one per query head) are given."""
     bs = cache.block_size
     if (out.dtype == torch.bfloat16 and plan is not None and bs & (bs - 1) == 0
             and attention_mma_supported(n_heads, n_kv_heads, head_dim, qkv.stride(0), out.stride(0))):
@@ -484,20 +530,22 @@ def attention(qkv, out, cache, step, plan, n_heads, n_kv_heads, head_dim, scale,
             if USE_TC_ATTENTION and attention_tc_supported(qkv, out, cache.k, cache.v, n_heads, n_kv_heads, head_dim):
                 row0, nrows, n = plan.tiles(tile_rows(1))
                 attention_prefill_tc(qkv, out, cache.k, cache.v, step.positions, step.seq_of_row, cache.tables,
-                                     row0, nrows, n, n_heads, n_kv_heads, head_dim, scale, window, err, softcap, sink)
+                                     row0, nrows, n, n_heads, n_kv_heads, head_dim, scale, window, err, softcap, sink,
+                                     sink_values)
             else:
                 row0, nrows, n = plan.tiles(tile_rows(0))
                 attention_prefill(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
                                   cache.tables, row0, nrows, n, n_heads, n_kv_heads, head_dim, scale, window, err,
-                                  softcap, sink)
+                                  softcap, sink, sink_values)
         if plan.n_decode:
             chunk, n_splits = plan.chunk(n_kv_heads, head_dim)
             attention_decode(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row,
                              cache.tables, plan.decode_rows, plan.n_decode, n_heads, n_kv_heads, head_dim, scale,
-                             window, chunk, n_splits, err, softcap, sink)
+                             window, chunk, n_splits, err, softcap, sink, sink_values)
         return
     attention_generic_v(qkv, qkv.stride(0), out, cache.k, cache.v, step.positions, step.seq_of_row, cache.tables,
-                        n_heads, n_kv_heads, head_dim, head_dim, scale, window, err, softcap=softcap, sink=sink)
+                        n_heads, n_kv_heads, head_dim, head_dim, scale, window, err, softcap=softcap, sink=sink,
+                        sink_values=sink_values)
 
 
 def scatter_int(dst, idx, val) -> None:
@@ -757,12 +805,15 @@ def gated_group_norm(y, z, weight, out, parts, eps) -> None:
 LATENT_MAX_RANK = 1024  # `cuca_latent_max_rank` says the same
 
 
-def latent_prepare(qkg, H, dn, dr, rank, c_gain, eps, cos, sin, rot_dims, qk, cache, step, err) -> None:
+def latent_prepare(qkg, H, dn, dr, rank, c_gain, eps, cos, sin, rot_dims, qk, cache, step, err,
+                   half_pairs: bool = False) -> None:
+    """Norms the latent, turns the shared key part and the heads' turned query parts by the row's position (pairs
+    (2i, 2i + 1), or (i, i + rot_dims / 2) with `half_pairs`) and writes the cache row."""
     lib = library.load()
     pool = cache.k
-    library.check(lib.cuca_latent_prepare(
+    library.check(lib.cuca_latent_prepare_p(
         _p(qkg), qkg.stride(0), H, dn, dr, rank, _p(c_gain), float(eps), _p(cos), _p(sin), cos.shape[0], int(rot_dims),
-        _p(qk), _p(pool), dtype_code(pool.dtype), pool.shape[0], pool.shape[2], _p(step.positions), _p(step.seq_of_row),
+        int(bool(half_pairs)), _p(qk), _p(pool), dtype_code(pool.dtype), pool.shape[0], pool.shape[2], _p(step.positions), _p(step.seq_of_row),
         _p(cache.tables), cache.tables.shape[1], qkg.shape[0], _p(err), _stream()), "latent_prepare")
 
 
@@ -786,20 +837,22 @@ def latent_attention_mma_supported(rank: int, Dk: int) -> bool:
     return _latent_mma_ok[key]
 
 
-def latent_attention(qk, out, cache, step, H, rank, Dk, scale, window, err) -> None:
+def latent_attention(qk, out, cache, step, H, rank, Dk, scale, window, err, sink_values=None) -> None:
     """Every row's heads attend over the cached rows of the row's request. A bfloat16 cache goes through the
     tensor-core form, portions of prompts in groups of 16 tokens per head and single tokens with their heads as the
-    group (the step's attention plan names both); the 32-bit path and other sizes go through the plain kernel."""
+    group (the step's attention plan names both); the 32-bit path and other sizes go through the plain kernel.
+    `sink_values` (32-bit, one number per head): every denominator holds one more term exp(sink_values[head])."""
     pool = cache.k
+    sink = _sink_values(sink_values, H)
     plan = attention_plan(step) if USE_MMA_LATENT and pool.dtype == torch.bfloat16 else None
     if plan is not None and latent_attention_mma_supported(rank, Dk):
         lib = library.load()
 
         def launch(row0, nrows, rows, n, splits=1, acc=None, ml=None):
-            library.check(lib.cuca_latent_attention_mma(
+            library.check(lib.cuca_latent_attention_mma_s(
                 _p(qk), _p(out), _p(pool), pool.shape[0], pool.shape[2], _p(step.positions), _p(step.seq_of_row),
                 _p(cache.tables), cache.tables.shape[1], _p(row0), _p(nrows), _p(rows), n, H, rank, Dk, float(scale),
-                int(window or 0), splits, _p(acc), _p(ml), _p(err), _stream()), "latent_attention_mma")
+                int(window or 0), sink, splits, _p(acc), _p(ml), _p(err), _stream()), "latent_attention_mma")
         if plan.n_portions:
             row0, nrows, n = plan.tiles(LATENT_TILE_ROWS)
             launch(row0, nrows, None, n)
@@ -817,10 +870,10 @@ def latent_attention(qk, out, cache, step, H, rank, Dk, scale, window, err) -> N
             else:
                 launch(None, None, plan.decode_rows, plan.n_decode)
         return
-    library.check(library.load().cuca_latent_attention(
+    library.check(library.load().cuca_latent_attention_s(
         _p(qk), _p(out), _p(pool), dtype_code(pool.dtype), pool.shape[0], pool.shape[2], _p(step.positions),
         _p(step.seq_of_row), _p(cache.tables), cache.tables.shape[1], qk.shape[0], H, rank, Dk, float(scale),
-        int(window or 0), _p(err), _stream()), "latent_attention")
+        int(window or 0), sink, _p(err), _stream()), "latent_attention")
 
 
 # ------------------------------------------------------------------ attention whose values are wider or narrower than its keys
@@ -840,31 +893,37 @@ def rope_store_general(qkv, k_col, v_col, positions, seq_of_row, tables, cos, si
 
 
 def attention_generic_v(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, n_heads, n_kv_heads,
-                        head_dim, v_head_dim, scale, window, err, softcap: float = 0.0, sink: bool = False) -> None:
+                        head_dim, v_head_dim, scale, window, err, softcap: float = 0.0, sink: bool = False,
+                        sink_values=None) -> None:
     """The plain attention kernel with value heads of their own size (`vpool`: [pages, kv heads, block, v_head_dim]).
-    `softcap` c > 0: a score s becomes c tanh(s / c); `sink`: the softmax's denominator holds one more exp(0)."""
+    `softcap` c > 0: a score s becomes c tanh(s / c); `sink`: the softmax's denominator holds one more exp(0), or
+    exp(sink_values[head]) when those are given."""
     _cuda(q, out, kpool, vpool)
-    library.check(library.load().cuca_attention_generic_s(
+    library.check(library.load().cuca_attention_generic_sv(
         _p(q), int(q_stride), _p(out), out.stride(0), dtype_code(out.dtype), _p(kpool), _p(vpool), kpool.shape[0],
         kpool.shape[2], _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], out.shape[0], n_heads,
         n_kv_heads, head_dim, v_head_dim, float(scale), int(window or 0), float(softcap or 0.0), int(bool(sink)),
-        _p(err), _stream()), "attention_generic")
+        _sink_values(sink_values, n_heads), _p(err), _stream()), "attention_generic")
 
 
 def norm_rope_store(qkv, k_col, v_col, positions, seq_of_row, tables, cos, sin, rotary_dim, adjacent, q_norm, k_norm,
                     v_norm: bool, eps: float, kpool, vpool, block_size, n_heads, n_kv_heads, head_dim, v_head_dim, err,
-                    v_split: int = 1, q_out=None, v_row_dim: int = 0) -> None:
+                    v_split: int = 1, q_out=None, v_row_dim: int = 0, whole: bool = False, q_temp=None) -> None:
     """`rope_store_general` with norms per head in 32-bit before the rotation: q / rms(q) * q_norm, k likewise with
     k_norm (None: no norm), and with `v_norm` v / rms(v) before it is kept. q is rewritten in place, or goes to
     `q_out` [rows, heads * head_dim] of the pools' dtype (32-bit rows beside 16-bit pools). `v_row_dim` n > 0: a row's
-    value heads hold n values (the norm is over those) and the pool's `v_head_dim` >= n; the rest is kept as zeros."""
+    value heads hold n values (the norm is over those) and the pool's `v_head_dim` >= n; the rest is kept as zeros.
+    `whole`: the norm of q (and of k) is over the whole projection, all heads at once, with weights [heads * head_dim].
+    `q_temp` (coef, every): the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1)."""
     _cuda(qkv, positions, seq_of_row, kpool, vpool, q_norm, k_norm, q_out)
-    library.check(library.load().cuca_norm_rope_store(
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+    library.check(library.load().cuca_norm_rope_store_w(
         _p(qkv), dtype_code(qkv.dtype), qkv.stride(0), int(k_col), int(v_col), _p(q_out), dtype_code(kpool.dtype),
         _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], _p(cos), _p(sin),
         cos.shape[0] if cos is not None else 0, int(rotary_dim), int(bool(adjacent)), _p(q_norm), _p(k_norm),
         int(bool(v_norm)), float(eps), _p(kpool), _p(vpool), kpool.shape[0], int(block_size), qkv.shape[0], n_heads,
-        n_kv_heads, head_dim, v_head_dim, int(v_split), int(v_row_dim), _p(err), _stream()), "norm_rope_store")
+        n_kv_heads, head_dim, v_head_dim, int(v_split), int(v_row_dim), int(bool(whole)), coef, every, _p(err),
+        _stream()), "norm_rope_store")
 
 
 def sigmoid_gate_(a, gate) -> None:
@@ -959,13 +1018,28 @@ def forget_scan(proj, q_col, f_col, v_col, f_bias, lower, state, out, step, H, d
     library.launches += 1
 
 
-def head_norm_gate(o, weight, per_head: bool, gate, out, H, dv, eps) -> None:
-    """out[r, h] = o[r, h] / rms(o[r, h]) * weight * sigmoid(gate[r, h]); weight [dv] for every head or [H dv]."""
+def retention_scan(proj, q_col, k_col, v_col, decay, cos, sin, rot_dims, k_scale, state, out, step, H, d, dv, err) -> None:
+    """Retention along every request's rows: S <- decay[h] S + k v^T, o = S^T q per head (see
+    `parts/recurrent.py:Retention`). The q and k columns of the 32-bit `proj` are rewritten in place before the scan
+    (the first `rot_dims` values of a head turned by the row's position in pairs (i, i + rot_dims / 2), k times
+    `k_scale`); two launches."""
+    _cuda(proj, decay, state, out, cos, sin)
+    library.check(library.load().cuca_retention_scan(
+        _p(proj), proj.stride(0), int(q_col), int(k_col), int(v_col), _p(decay), _p(cos), _p(sin),
+        cos.shape[0] if cos is not None else 0, int(rot_dims), float(k_scale), _p(step.positions), _p(state), _p(out),
+        _p(step.seq_of_row), _p(step.req_row0), _p(step.req_count), _p(step.slots), proj.shape[0], step.n_seqs, H, d, dv,
+        _p(err), _stream()), "retention_scan")
+    library.launches += 1
+
+
+def head_norm_gate(o, weight, per_head: bool, gate, out, H, dv, eps, gate_act: str = "sigmoid") -> None:
+    """out[r, h] = o[r, h] / rms(o[r, h]) * weight * act(gate[r, h]); weight [dv] for every head or [H dv], or None;
+    act the sigmoid or, `gate_act` "silu", g sigmoid(g)."""
     _cuda(o, weight, gate, out)
-    library.check(library.load().cuca_head_norm_gate(
+    library.check(library.load().cuca_head_norm_gate_act(
         _p(o), _p(weight), dv if per_head else 0, _p(gate), dtype_code(gate.dtype) if gate is not None else 0,
-        gate.stride(0) if gate is not None else 0, _p(out), dtype_code(out.dtype), o.shape[0], H, dv, float(eps),
-        _stream()), "head_norm_gate")
+        gate.stride(0) if gate is not None else 0, 1 if gate_act == "silu" else 0, _p(out), dtype_code(out.dtype),
+        o.shape[0], H, dv, float(eps), _stream()), "head_norm_gate")
 
 
 # ------------------------------------------------------------------ routed feed-forward

@@ -25,6 +25,13 @@ Values of a size that is no multiple of the keys' are kept padded with zeros to 
 tensor-core kernels take the rest of the shape (bfloat16, key sizes in steps of 16 up to 128, no output gate): the pool's
 rows, the attention output and the output projection's input columns (zero columns, added at load) are that wide, and
 the layer runs slab by slab like one whose values are a multiple. The norm on values is over the stored ones.
+
+Three more options of the general path. `qk_norm` "whole": the RMS norm of q (and of k) is taken over the whole
+projection, all heads at once, with a weight of that size (`q_norm` [heads * head_dim], `k_norm` [kv heads * head_dim]).
+`q_temp` {coef, every}: the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1) (after norm
+and rotation). `sink` "learned": the sink's score is a stored number per query head (`sink` [heads], neither scaled nor
+capped) instead of 0. `gate` "head": one gate per head, sigmoid(W_g h)_a with `g` [heads, width], multiplies head a's
+output.
 """
 from __future__ import annotations
 
@@ -40,9 +47,10 @@ from .base import POSITIONS, CacheNeeds, KvNeeds, Mixer, PartSpec, TensorNeed, r
 @register_mixer("attention")
 class PagedAttention(Mixer):
     """params: width, n_heads, n_kv_heads, head_dim, window (None: all keys), scale (None: 1/sqrt(head_dim)),
-    position (PartSpec or None), shares_cache (bool), v_head_dim (None: head_dim), gate (bool), qk_norm (bool),
-    v_norm (bool), eps (of those norms), softcap (None or 0: none), sink (bool). tensors: q, k, v, o, g (with `gate`),
-    q_norm and k_norm [head_dim] (with `qk_norm`) and optional q_bias, k_bias, v_bias, o_bias."""
+    position (PartSpec or None), shares_cache (bool), v_head_dim (None: head_dim), gate (bool, or "head"), qk_norm
+    (bool, or "whole"), v_norm (bool), eps (of those norms), softcap (None or 0: none), sink (bool, or "learned"),
+    q_temp ({coef, every} or None). tensors: q, k, v, o, g (with `gate`), q_norm and k_norm (with `qk_norm`), sink
+    (with a learned sink) and optional q_bias, k_bias, v_bias, o_bias."""
 
     graph_safe = True
 
@@ -57,11 +65,20 @@ class PagedAttention(Mixer):
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.head_dim)
         self.shares_cache = bool(p.get("shares_cache", False))
         self.v_head_dim = int(p["v_head_dim"]) if p.get("v_head_dim") else self.head_dim
-        self.gated = bool(p.get("gate", False))
+        self.head_gate = p.get("gate") == "head"  # one gate per head instead of one per value
+        self.gated = bool(p.get("gate", False)) and not self.head_gate
         self.qk_norm, self.v_norm = bool(p.get("qk_norm", False)), bool(p.get("v_norm", False))
+        self.norm_whole = p.get("qk_norm") == "whole"  # over the whole projection instead of per head
         self.eps = float(p.get("eps", 1e-6))
         self.softcap = float(p.get("softcap") or 0.0)
         self.sink = bool(p.get("sink", False))
+        self.sink_learned = p.get("sink") == "learned"
+        qt = p.get("q_temp")
+        self.q_temp = (float(qt["coef"]), int(qt["every"])) if qt else None
+        if self.q_temp is not None and self.q_temp[1] < 1:
+            raise ValueError(f"attention: a query temperature every {self.q_temp[1]} positions is not positive")
+        if self.norm_whole and self.v_norm:
+            raise ValueError("attention: a norm over the whole projection is not combined with a norm on values")
         if self.softcap < 0:
             raise ValueError(f"attention: a score cap of {self.softcap} is not positive")
         if self.n_heads % self.n_kv_heads:
@@ -71,11 +88,11 @@ class PagedAttention(Mixer):
                              f"(1..{ops.ATTENTION_MAX_HEAD_DIM})")
         pos = p.get("position")
         self.position = POSITIONS.get(pos.kind)(pos, runtime) if isinstance(pos, PartSpec) else None
-        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.w_qn = self.w_kn = None
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.w_qn = self.w_kn = self.sink_values = None
         # what the stacked-projection kernels of the usual path do not take
-        self.normed = self.qk_norm or self.v_norm
-        self.general = (self.v_head_dim != self.head_dim or self.gated or self.normed or self.softcap > 0 or self.sink
-                        or getattr(self.position, "pairs", "half") != "half")
+        self.normed = self.qk_norm or self.v_norm or self.q_temp is not None
+        self.general = (self.v_head_dim != self.head_dim or self.gated or self.head_gate or self.normed
+                        or self.softcap > 0 or self.sink or getattr(self.position, "pairs", "half") != "half")
         if self.general and self.shares_cache:
             raise ValueError("attention: a layer that reads another layer's pages takes neither a value size of its "
                              "own, an output gate, head norms, a score cap, a sink nor adjacent rotation pairs")
@@ -100,27 +117,37 @@ class PagedAttention(Mixer):
                t["o"]: TensorNeed((self.width, self.n_heads * dv))}
         if self.gated:
             out[t["g"]] = TensorNeed((self.n_heads * dv, self.width))
+        if self.head_gate:
+            out[t["g"]] = TensorNeed((self.n_heads, self.width))
         if self.qk_norm:
-            out[t["q_norm"]] = TensorNeed((d,), keep_fp32=True, init="ones")
-            out[t["k_norm"]] = TensorNeed((d,), keep_fp32=True, init="ones")
+            whole = self.norm_whole
+            out[t["q_norm"]] = TensorNeed((self.n_heads * d if whole else d,), keep_fp32=True, init="ones")
+            out[t["k_norm"]] = TensorNeed((self.n_kv_heads * d if whole else d,), keep_fp32=True, init="ones")
+        if self.sink_learned:
+            out[t["sink"]] = TensorNeed((self.n_heads,), keep_fp32=True)
         if not self.shares_cache:
             out[t["k"]] = TensorNeed((self.n_kv_heads * d, self.width))
             out[t["v"]] = TensorNeed((self.n_kv_heads * dv, self.width))
         for role, rows in (("q_bias", self.n_heads * d), ("k_bias", self.n_kv_heads * d),
-                           ("v_bias", self.n_kv_heads * d), ("o_bias", self.width)):
+                           ("v_bias", self.n_kv_heads * dv), ("o_bias", self.width)):
             if role in t and not (self.shares_cache and role in ("k_bias", "v_bias")):
                 out[t[role]] = TensorNeed((rows,), optional=True)
         return out
 
     def load(self, get):
         t = self.spec.tensors
-        roles = ["q"] if self.shares_cache else ["q", "k", "v"] + (["g"] if self.gated else [])
-        self.w_qkv = torch.cat([get(t[r]) for r in roles], dim=0).contiguous()
+        roles = ["q"] if self.shares_cache else ["q", "k", "v"] + (["g"] if self.gated or self.head_gate else [])
+        stacked = [get(t[r]) for r in roles]
         biases = [get(t[r + "_bias"]) if r + "_bias" in t else None for r in roles]
+        rows = sum(w.shape[0] for w in stacked)
+        if self.head_gate and rows % 8:  # rows of no weight, so that a projected row stays a multiple of 16 bytes
+            stacked.append(stacked[0].new_zeros(8 - rows % 8, self.width))
+            biases.append(None)
+        self.w_qkv = torch.cat(stacked, dim=0).contiguous()
         if any(b is not None for b in biases):
             if any(b is None for b in biases[:3]):
                 raise ValueError("attention biases must be given for q, k and v together")
-            biases = [b if b is not None else biases[0].new_zeros(get(t[r]).shape[0]) for b, r in zip(biases, roles)]
+            biases = [b if b is not None else biases[0].new_zeros(w.shape[0]) for b, w in zip(biases, stacked)]
             self.b_qkv = torch.cat(biases).contiguous()
         self.w_o = get(t["o"])
         if self.v_pool_dim != self.v_head_dim:  # zero columns where the padded attention output holds zeros
@@ -131,10 +158,12 @@ class PagedAttention(Mixer):
         self.b_o = get(t["o_bias"]) if "o_bias" in t else None
         if self.qk_norm:
             self.w_qn, self.w_kn = get(t["q_norm"]), get(t["k_norm"])
+        if self.sink_learned:
+            self.sink_values = get(t["sink"]).contiguous()
 
     def weight_bytes(self):
-        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o, self.b_qkv, self.b_o, self.w_qn, self.w_kn)
-                   if w is not None)
+        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o, self.b_qkv, self.b_o, self.w_qn, self.w_kn,
+                                                          self.sink_values) if w is not None)
 
     def prepare(self, context_length: int) -> None:
         if self.position is not None:
@@ -176,27 +205,32 @@ class PagedAttention(Mixer):
         if self.normed:
             ops.norm_rope_store(proj, nh * d, (nh + nkv) * d, step.positions, step.seq_of_row, cache.tables, cos, sin,
                                 rot, adjacent, self.w_qn, self.w_kn, self.v_norm, self.eps, cache.k, cache.v,
-                                cache.block_size, nh, nkv, d, dv, self.rt.err, v_split=split, v_row_dim=dv_row)
+                                cache.block_size, nh, nkv, d, dv, self.rt.err, v_split=split, v_row_dim=dv_row,
+                                whole=self.norm_whole, q_temp=self.q_temp)
         else:
             ops.rope_store_general(proj, nh * d, (nh + nkv) * d, step.positions, step.seq_of_row, cache.tables, cos, sin,
                                    rot, adjacent, cache.k, cache.v, cache.block_size, nh, nkv, d, dv, self.rt.err,
                                    v_split=split, v_row_dim=dv_row)
-        gate = proj[:, (nh + nkv) * d + nkv * dv:] if self.gated else None  # (a gated layer is never padded)
+        g_col = (nh + nkv) * d + nkv * self.v_head_dim
+        gate = proj[:, g_col:] if self.gated else None  # (a layer with a gate per value is never padded)
         attn = self.rt.empty(rows, nh * dv)
         if tensor_cores:
             slabs = cache.v.view(split, *cache.k.shape)
             parts = self.rt.empty(split, rows, nh * d) if (split > 1 or gate is not None) else attn.view(1, rows, nh * d)
             for j in range(split):
                 ops.attention(proj, parts[j], dataclasses.replace(cache, v=slabs[j]), step, plan, nh, nkv, d, self.scale,
-                              self.window, self.rt.err, softcap=self.softcap, sink=self.sink)
+                              self.window, self.rt.err, softcap=self.softcap, sink=self.sink,
+                              sink_values=self.sink_values)
             if parts.data_ptr() != attn.data_ptr():
                 ops.gate_merge(parts, gate, attn, nh, dv)
         else:
             ops.attention_generic_v(proj, proj.stride(0), attn, cache.k, cache.v, step.positions, step.seq_of_row,
                                     cache.tables, nh, nkv, d, dv, self.scale, self.window, self.rt.err,
-                                    softcap=self.softcap, sink=self.sink)
+                                    softcap=self.softcap, sink=self.sink, sink_values=self.sink_values)
             if gate is not None:
                 ops.sigmoid_gate_(attn, gate)
+        if self.head_gate:
+            ops.head_gate_(attn, proj[:, g_col:g_col + nh], nh, dv)
         stream.add_linear(attn, self.w_o, bias=self.b_o)
 
     def forward(self, h, stream, step, cache) -> None:

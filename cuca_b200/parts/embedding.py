@@ -13,34 +13,49 @@ from .base import Part, TensorNeed
 
 
 class TokenEmbedding(Part):
-    """params: vocab, width, scale (a factor on every embedding row, default 1). tensors: weight [vocab, width]."""
+    """params: vocab, width, scale (a factor on every embedding row, default 1), norm_eps (None: none; a number: the
+    row is RMS-normed, e / sqrt(mean(e^2) + norm_eps) times the tensor `norm`, before it becomes the stream).
+    tensors: weight [vocab, width], norm [width] (with norm_eps)."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.vocab = int(spec.params["vocab"])
         self.width = int(spec.params["width"])
         self.scale = float(spec.params.get("scale", 1.0))
-        self.weight = None
+        eps = spec.params.get("norm_eps")
+        self.norm_eps = float(eps) if eps is not None else None
+        self.weight = self.norm_weight = None
 
     def tensors(self):
-        return {self.spec.tensors["weight"]: TensorNeed((self.vocab, self.width))}
+        out = {self.spec.tensors["weight"]: TensorNeed((self.vocab, self.width))}
+        if self.norm_eps is not None:
+            out[self.spec.tensors["norm"]] = TensorNeed((self.width,), keep_fp32=True, init="ones")
+        return out
 
     def load(self, get):
         self.weight = get(self.spec.tensors["weight"])
+        if self.norm_eps is not None:
+            self.norm_weight = get(self.spec.tensors["norm"])
 
     def forward(self, tokens, out) -> None:
-        ops.embed(self.weight, tokens, out, self.rt.err, self.scale)
+        if self.norm_eps is not None:
+            ops.embed_norm(self.weight, tokens, out, self.norm_weight, self.norm_eps, self.rt.err, self.scale)
+        else:
+            ops.embed(self.weight, tokens, out, self.rt.err, self.scale)
 
 
 class OutputHead(Part):
-    """params: vocab, width, scale (a factor on the logits, default 1). tensors: weight [vocab, width] (the
-    embedding's name when tied)."""
+    """params: vocab, width, scale (a factor on the logits, default 1), softcap (None or 0: none; c > 0: the logits
+    become c tanh(logits / c), after the scale). tensors: weight [vocab, width] (the embedding's name when tied)."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.vocab = int(spec.params["vocab"])
         self.width = int(spec.params["width"])
         self.scale = float(spec.params.get("scale", 1.0))
+        self.softcap = float(spec.params.get("softcap") or 0.0)
+        if self.softcap < 0:
+            raise ValueError(f"output head: a cap of {self.softcap} on the logits is not positive")
         self.weight = None
 
     def tensors(self):
@@ -56,4 +71,6 @@ class OutputHead(Part):
         logits = self.rt.linear(h, self.weight, out_dtype=torch.float32)
         if self.scale != 1.0:
             ops.scale_(logits, self.scale)
+        if self.softcap > 0:
+            ops.softcap_(logits, self.softcap)
         return logits

@@ -80,6 +80,48 @@ class CappedGLU(FeedForward):
         self.rt.stream(stream).add_linear(act, self.w_down)
 
 
+@register_feed_forward("glu")
+class GatedUnit(FeedForward):
+    """y = down(act(gate f) * (up f)) with act the silu or the tanh form of gelu,
+    0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))). gate and up are stacked into one weight at load.
+    params: width, inner, act ("silu" | "gelu_tanh"). tensors: gate [inner, width], up [inner, width],
+    down [width, inner]."""
+
+    graph_safe = True
+    ACTS = {"silu": ops.GLU_SILU, "gelu_tanh": ops.GLU_GELU_TANH}
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.width, self.inner = int(spec.params["width"]), int(spec.params["inner"])
+        act = str(spec.params.get("act", "silu"))
+        if act not in self.ACTS:
+            raise ValueError(f"gated feed-forward: activation `{act}` is unknown; known: {', '.join(sorted(self.ACTS))}")
+        self.act = self.ACTS[act]
+        self.w_gate_up = self.w_down = None
+
+    def tensors(self):
+        t = self.spec.tensors
+        return {t["gate"]: TensorNeed((self.inner, self.width)), t["up"]: TensorNeed((self.inner, self.width)),
+                t["down"]: TensorNeed((self.width, self.inner))}
+
+    def load(self, get):
+        t = self.spec.tensors
+        self.w_gate_up = torch.cat([get(t["gate"]), get(t["up"])], dim=0).contiguous()
+        self.w_down = get(t["down"])
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_gate_up, self.w_down))
+
+    def forward(self, h, stream, step) -> None:
+        if self.act == ops.GLU_SILU:  # the contraction's own epilogue
+            act = self.rt.linear(h, self.w_gate_up, epilogue=ops.EPI_SWIGLU)
+        else:
+            gu = self.rt.linear(h, self.w_gate_up)
+            act = self.rt.empty(h.shape[0], self.inner)
+            ops.glu_act(gu, act, self.act)
+        self.rt.stream(stream).add_linear(act, self.w_down)
+
+
 @register_feed_forward("dense_act")
 class DenseActivation(FeedForward):
     """y = down(act(up f + b_up)) + b_down with act the exact (erf) GELU or its tanh form.
@@ -130,9 +172,13 @@ class RoutedExperts(FeedForward):
     experts * inner]). Many tokens: all experts' up-projections in one contraction, the activation weighted per
     expert (0 for the ones a token did not choose), one contraction over (expert, inner) down. Few tokens: only the
     chosen experts' rows are read, a warp per output. Both sum a token's experts in a fixed order.
+    With act "swiglu" the experts are gated, down_e(silu(gate_e f) * (up_e f)): the gates and ups are stacked as
+    `up` [2 experts * inner, width] (every expert's gate rows, then every expert's up rows). With `router_bias` the
+    logits are z = W_r f + b.
 
-    params: width, inner, experts, top, act ("relu2"). tensors: router [experts, width], `up{e}` [inner, width] and
-    `down{e}` [width, inner] for every expert e."""
+    params: width, inner, experts, top, act ("relu2" | "swiglu"), router_bias (bool). tensors: router [experts, width],
+    router_bias [experts], `up{e}` [inner, width] and `down{e}` [width, inner] for every expert e, and with "swiglu"
+    `gate{e}` [inner, width]."""
 
     graph_safe = True
     SPARSE_MAX_TOKENS = 32  # up to this many tokens only the chosen experts are read
@@ -142,17 +188,24 @@ class RoutedExperts(FeedForward):
         p = spec.params
         self.width, self.inner = int(p["width"]), int(p["inner"])
         self.experts, self.top = int(p["experts"]), int(p["top"])
-        if str(p.get("act", "relu2")) != "relu2":
-            raise ValueError(f"routed feed-forward: activation `{p.get('act')}` is unknown; known: relu2")
+        act = str(p.get("act", "relu2"))
+        if act not in ("relu2", "swiglu"):
+            raise ValueError(f"routed feed-forward: activation `{act}` is unknown; known: relu2, swiglu")
+        self.glu = act == "swiglu"
+        self.router_bias = bool(p.get("router_bias", False))
         if not 1 <= self.top <= min(self.experts, ops.MOE_MAX_TOP) or self.experts > ops.MOE_MAX_EXPERTS:
             raise ValueError(f"routed feed-forward: {self.top} of {self.experts} experts is outside what the kernels "
                              f"take (experts <= {ops.MOE_MAX_EXPERTS}, chosen <= {ops.MOE_MAX_TOP})")
-        self.w_router = self.w_up = self.w_down = None
+        self.w_router = self.b_router = self.w_up = self.w_down = None
 
     def tensors(self):
         t = self.spec.tensors
         out = {t["router"]: TensorNeed((self.experts, self.width))}
+        if self.router_bias:
+            out[t["router_bias"]] = TensorNeed((self.experts,))
         for e in range(self.experts):
+            if self.glu:
+                out[t[f"gate{e}"]] = TensorNeed((self.inner, self.width))
             out[t[f"up{e}"]] = TensorNeed((self.inner, self.width))
             out[t[f"down{e}"]] = TensorNeed((self.width, self.inner))
         return out
@@ -160,29 +213,38 @@ class RoutedExperts(FeedForward):
     def load(self, get):
         t = self.spec.tensors
         self.w_router = get(t["router"])
-        self.w_up = torch.cat([get(t[f"up{e}"]) for e in range(self.experts)], dim=0).contiguous()
+        if self.router_bias:
+            self.b_router = get(t["router_bias"])
+        gates = [get(t[f"gate{e}"]) for e in range(self.experts)] if self.glu else []
+        self.w_up = torch.cat(gates + [get(t[f"up{e}"]) for e in range(self.experts)], dim=0).contiguous()
         self.w_down = torch.cat([get(t[f"down{e}"]) for e in range(self.experts)], dim=1).contiguous()
 
     def weight_bytes(self):
         """What a step of several tokens reads at most: the router and every expert once."""
-        return sum(w.numel() * w.element_size() for w in (self.w_router, self.w_up, self.w_down))
+        return sum(w.numel() * w.element_size() for w in (self.w_router, self.b_router, self.w_up, self.w_down)
+                   if w is not None)
 
     def forward(self, h, stream, step) -> None:
         rt, T = self.rt, h.shape[0]
-        logits = rt.linear(h, self.w_router, out_dtype=torch.float32)
+        logits = rt.linear(h, self.w_router, bias=self.b_router, out_dtype=torch.float32)
         idx = torch.empty(T, self.top, dtype=torch.int32, device=rt.device)
         wts = torch.empty(T, self.top, dtype=torch.float32, device=rt.device)
         if T <= self.SPARSE_MAX_TOKENS:
             ops.moe_route(logits, self.top, idx, wts)
             a = rt.empty(T * self.top, self.inner)
             y, fresh = rt.stream(stream).claim()
-            ops.moe_sparse(h, self.w_up, self.w_down, idx, wts, a, y, fresh, self.top, self.experts, self.inner)
+            ops.moe_sparse(h, self.w_up, self.w_down, idx, wts, a, y, fresh, self.top, self.experts, self.inner,
+                           glu=self.glu)
             return
         spread = torch.empty(T, self.experts, dtype=torch.float32, device=rt.device)
         ops.moe_route(logits, self.top, idx, wts, spread)
         u = rt.linear(h, self.w_up)
-        a = torch.empty_like(u)
-        ops.moe_act_dense(u, spread, a, self.experts, self.inner)
+        if self.glu:
+            a = rt.empty(T, self.experts * self.inner)
+            ops.moe_glu_dense(u, spread, a, self.experts * self.inner, self.inner)
+        else:
+            a = torch.empty_like(u)
+            ops.moe_act_dense(u, spread, a, self.experts, self.inner)
         rt.stream(stream).add_linear(a, self.w_down)
 
 

@@ -10,7 +10,8 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import CacheNeeds, Mixer, StateNeeds, TensorNeed, register_mixer
+from . import rope  # noqa: F401  (registers the rotary tables the retention mixer asks for)
+from .base import POSITIONS, CacheNeeds, Mixer, PartSpec, StateNeeds, TensorNeed, register_mixer
 
 
 @register_mixer("mingru")
@@ -322,4 +323,69 @@ class ForgetGateAttention(Mixer):
         ops.forget_scan(proj, 0, H * d, 2 * H * d, self.f_bias, self.lower, cache.state["memory"], o, step, H, d, dv)
         out = rt.empty(rows, H * dv)
         ops.head_norm_gate(o, self.norm_w, False, None, out, H, dv, self.eps)
+        rt.stream(stream).add_linear(out, self.w_o)
+
+
+@register_mixer("retention")
+class Retention(Mixer):
+    """Retention: linear attention with one fixed decay per head, no softmax and no denominator. q = W_q h, k = W_k h
+    (heads x dim), v = W_v h (heads x vdim); the first rotated dimensions of every q and k head turn by the position
+    (the position part's tables, pairs (i, i + n/2)), then k is multiplied by dim^(-1/2); per head, S of dim x vdim
+    (zero at the start):
+        S <- decay_a S + k v^T;   o = S^T q;
+    o / rms(o) per head (no weight), the concatenated heads times silu(W_g h), then W_o. State: S in 32-bit.
+    params: width, heads, dim, vdim, decay (one number per head), eps, position (a rotary PartSpec or None).
+    tensors: q, k, v, g, o."""
+
+    graph_safe = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.width, self.heads = int(p["width"]), int(p["heads"])
+        self.dim, self.vdim, self.eps = int(p["dim"]), int(p["vdim"]), float(p["eps"])
+        self.decay_values = [float(v) for v in p["decay"]]
+        if len(self.decay_values) != self.heads:
+            raise ValueError(f"retention: {len(self.decay_values)} decays for {self.heads} heads")
+        if self.dim > ops.MATRIX_STATE_MAX_DIM:
+            raise ValueError(f"retention: {self.dim} key channels exceed {ops.MATRIX_STATE_MAX_DIM}")
+        pos = p.get("position")
+        self.position = POSITIONS.get(pos.kind)(pos, runtime) if isinstance(pos, PartSpec) else None
+        if self.position is not None and self.position.pairs != "half":
+            raise ValueError("retention: rotated dimensions pair as (i, i + n/2)")
+        self.w_in = self.w_o = self.decay = None
+
+    def cache_needs(self):
+        return CacheNeeds(state={"memory": StateNeeds((self.heads, self.vdim, self.dim))})
+
+    def tensors(self):
+        t, E, H = self.spec.tensors, self.width, self.heads
+        return {t["q"]: TensorNeed((H * self.dim, E)), t["k"]: TensorNeed((H * self.dim, E)),
+                t["v"]: TensorNeed((H * self.vdim, E)), t["g"]: TensorNeed((H * self.vdim, E)),
+                t["o"]: TensorNeed((E, H * self.vdim))}
+
+    def load(self, get):
+        t = self.spec.tensors
+        self.w_in = torch.cat([get(t[r]) for r in ("q", "k", "v", "g")], dim=0).contiguous()
+        self.w_o = get(t["o"])
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=self.rt.device)
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_o))
+
+    def prepare(self, context_length: int) -> None:
+        if self.position is not None:
+            self.position.prepare(context_length)
+
+    def forward(self, h, stream, step, cache) -> None:
+        rt, rows = self.rt, h.shape[0]
+        H, d, dv = self.heads, self.dim, self.vdim
+        proj = rt.linear(h, self.w_in, out_dtype=torch.float32)  # [q | k | v | g]
+        cos, sin, rot = (self.position.cos, self.position.sin, self.position.rotary_dim) \
+            if self.position is not None else (None, None, 0)
+        o = rt.empty(rows, H * dv, dtype=torch.float32)
+        ops.retention_scan(proj, 0, H * d, 2 * H * d, self.decay, cos, sin, rot, d ** -0.5, cache.state["memory"], o,
+                           step, H, d, dv, rt.err)
+        out = rt.empty(rows, H * dv)
+        ops.head_norm_gate(o, None, False, proj[:, 2 * H * d + H * dv:], out, H, dv, self.eps, gate_act="silu")
         rt.stream(stream).add_linear(out, self.w_o)
