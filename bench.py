@@ -249,6 +249,30 @@ def _pudinex_config(width, ff, heads, layers, vocab, window):
             "layers": [dict(attention if i % 3 == 2 else forget, mlp=dense if i == 0 else routed) for i in range(layers)]}
 
 
+def _sutosun_config(width, ff, heads, layers, vocab, window):
+    """`layers` layers in turns of three: latent attention (heads of 128 + 64 rotated dimensions, a latent of 512, YaRN,
+    a sink per head), softmax attention without rotation (heads of 128, a quarter as many key heads, a norm over the
+    whole q and k projections, a query temperature, a sink and a gate per head) and retention (heads of 128 x 128, half
+    of a head rotated); the first layer's feed-forward is the dense gated GELU unit, the others are routed (eight gated
+    experts of ff / 4, two chosen). `window` is unused: the design has none."""
+    H = max(1, width // 128)
+    latent = {"type": "latent_attention",
+              "mixer": {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+                        "rot": {"base": 10000.0, "dims": 64,
+                                "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    attention = {"type": "attention",
+                 "mixer": {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                           "q_temp": {"coef": 0.1, "every": 1024}}}
+    retention = {"type": "retention",
+                 "mixer": {"heads": H, "dim": 128, "vdim": 128, "rot": {"base": 10000.0, "dims": 64},
+                           "decay": [1.0 - 2.0 ** -(5 + a % 8) for a in range(H)]}}
+    routed = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 8, "top": 2}}
+    dense = {"kind": "dense", "ff": ff}
+    return {"architecture": "Sutosun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "layers": [dict((latent, attention, retention)[i % 3], mlp=dense if i == 0 else routed)
+                       for i in range(layers)]}
+
+
 def _llama_config(width, ff, heads, layers, vocab):
     return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers,
             "hidden_size": width, "num_attention_heads": heads, "num_key_value_heads": max(1, heads // 4),
@@ -263,8 +287,9 @@ DESIGN_SIZES = {  # name -> (width, feed-forward, heads, layers, vocabulary)
 
 def design_table(args) -> int:
     """Prefill of one prompt and decode steps of `--batch` requests for the chosen design and for a Llama of the
-    same width, feed-forward size and number of layer runs, one JSON line per size and model: tokens/s of both
-    phases, the decode step's bytes (weights once, what a request keeps) over the measured copy bandwidth."""
+    same width, feed-forward size and number of layer runs (for Sutosun: a Pudinex, the closest of the other designs,
+    and the Llama), one JSON line per size and model: tokens/s of both phases, the decode step's bytes (weights once,
+    what a request keeps) over the measured copy bandwidth."""
     import numpy as np
     import torch
 
@@ -278,10 +303,14 @@ def design_table(args) -> int:
     ctx = max(T, P + steps + warmup + 64) + 64
     for size in (args.sizes.split(",") if args.sizes else list(DESIGN_SIZES)):
         width, ff, heads, layers, vocab = DESIGN_SIZES[size]
-        runs = layers if args.design == "pudinex" else layers + layers // 2  # (a looped half runs twice)
-        make = {"bananex": _bananex_config, "dupenex": _dupenex_config, "pudinex": _pudinex_config}[args.design]
-        for name, cfg in ((args.design, make(width, ff, heads, layers, vocab, window=1024)),
-                          ("llama", _llama_config(width, ff, heads, runs, vocab))):
+        runs = layers if args.design in ("pudinex", "sutosun") else layers + layers // 2  # (a looped half runs twice)
+        make = {"bananex": _bananex_config, "dupenex": _dupenex_config, "pudinex": _pudinex_config,
+                "sutosun": _sutosun_config}[args.design]
+        pair = [(args.design, make(width, ff, heads, layers, vocab, window=1024))]
+        if args.design == "sutosun":
+            pair.append(("pudinex", _pudinex_config(width, ff, heads, layers, vocab, window=1024)))
+        pair.append(("llama", _llama_config(width, ff, heads, runs, vocab)))
+        for name, cfg in pair:
             if args.only_model and name != args.only_model:
                 continue
             model = LocalModel.load(LocalModelConfig(
@@ -368,7 +397,7 @@ def main() -> int:
     ap.add_argument("--decode-only", action="store_true",
                     help="with --shape llama-3.2-1b: the plain decode line at --batch instead of the mixed workload")
     ap.add_argument("--only-model", default=None, help="with --design: run only this model of the pair (the design's name or llama)")
-    ap.add_argument("--design", default=None, choices=["bananex", "dupenex", "pudinex"],
+    ap.add_argument("--design", default=None, choices=["bananex", "dupenex", "pudinex", "sutosun"],
                     help="instead of the bench: prefill and decode of this design beside a Llama of equal width, "
                          "feed-forward size and layer runs, at --sizes (1b,3b,8b layer sizes; a few layers each)")
     ap.add_argument("--sizes", default=None, help="with --design: which of 1b,3b,8b (all else)")

@@ -69,8 +69,8 @@ struct Params {
   int ordered_add;  // mode 2 into the 32-bit stream over many tokens: the K slices of a tile add themselves in turn
   int skew;         // ... and slice k + 1 has `skew` K steps more than slice k, so that it finishes when slice k has added
   int slab_rows;    // pairs of CTAs leaving K slices unadded: rows of one slice's slab in `out` (a multiple of 32, >= M)
-  // the gated epilogue: limit <= 0: silu(g) u; limit > 0: g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
-  // u' = clamp(u, -limit, limit)
+  // the gated epilogue: limit = 0: silu(g) u; limit > 0: g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
+  // u' = clamp(u, -limit, limit); limit < 0: gelu(g) u with the tanh form of gelu
   float glu_limit, glu_alpha;
 };
 
@@ -202,6 +202,11 @@ __device__ __forceinline__ float glu_act(const Params& p, float g, float u) {
     g = fminf(g, p.glu_limit);
     u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit);
     return __fdividef(g, 1.f + __expf(-p.glu_alpha * g)) * (u + 1.f);
+  }
+  if (p.glu_limit < 0.f) {
+    // 0.5 g (1 + tanh(y)) = g sigmoid(2 y) with y = sqrt(2/pi) (g + 0.044715 g^3)
+    const float y2 = 1.5957691216057308f * (g + 0.044715f * g * g * g);
+    return __fdividef(g, 1.f + __expf(-y2)) * u;
   }
   return silu_mul(g, u);
 }
@@ -1306,6 +1311,16 @@ CUCA_API int cuca_gemm_tc_glu(const void* A, const void* W, void* out, int M, in
                       n_counters, max_splits, nullptr, err, stream, limit, alpha);
 }
 
+
+// The gated epilogue with a chosen activation: act 0: silu(g) u, 1: gelu(g) u with the tanh form of gelu,
+// 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+CUCA_API int cuca_gemm_tc_glu_act(const void* A, const void* W, void* out, int M, int N, int K, int lda, int ldo, int act,
+                                  void* workspace, size_t ws_bytes, int* counters, int n_counters, int max_splits,
+                                  int* err, cudaStream_t stream) {
+  CUCA_REQUIRE(act == 0 || act == 1, "gemm_tc_glu_act: unknown activation %d", act);
+  return gemm_tc_impl(A, W, nullptr, out, CUCA_BF16, M, N, K, lda, ldo, EPI_SWIGLU, workspace, ws_bytes, counters,
+                      n_counters, max_splits, nullptr, err, stream, act == 1 ? -1.f : 0.f, 1.f);
+}
 
 CUCA_API int cuca_gemm_tc_partial_max_tokens() { return pair_partial_takes(PAIR_PARTIAL_MAX_TOKENS, 4) ? PAIR_PARTIAL_MAX_TOKENS : SWAP_MAX_TOKENS; }
 

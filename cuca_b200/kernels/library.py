@@ -121,6 +121,7 @@ _SIGNATURES = {
                              _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "cuca_forget_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "cuca_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, c_size_t, _P, _I, _I, _P, _P],
+    "cuca_gemm_tc_glu_act": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, c_size_t, _P, _I, _I, _P, _P],
     "cuca_embed_norm": [_P, _I, _P, _P, _I, _I, _I, _F, _P, _F, _P, _P],
     "cuca_glu_act": [_P, _P, _I, _I, _I, _I, _P],
     "cuca_head_gate": [_P, _I, _P, _I, _I, _I, _I, _I, _P],

@@ -226,6 +226,18 @@ def gemm_tc_glu(a, w, out, limit: float, alpha: float, err=None, max_splits=16) 
                                        counters.numel(), int(max_splits), _p(err), _stream()), "gemm_tc_glu")
 
 
+def gemm_tc_glu_act(a, w, out, act: int, err=None, max_splits=16) -> None:
+    """out = act(g) * u of [g | u] = a @ w.T (w: gate rows, then up rows) as the contraction's epilogue, from the
+    32-bit sums; act: GLU_SILU or GLU_GELU_TANH."""
+    _cuda(a, w, out)
+    lib = library.load()
+    M, K = a.shape
+    ws, counters = gemm_scratch(a.device)
+    library.check(lib.cuca_gemm_tc_glu_act(_p(a), _p(w), _p(out), M, out.shape[1], K, a.stride(0), out.stride(0),
+                                           int(act), _p(ws), ws.numel() * 4, _p(counters), counters.numel(),
+                                           int(max_splits), _p(err), _stream()), "gemm_tc_glu_act")
+
+
 def gemm_pair_mode(mode: int) -> None:
     """When contractions over many tokens run as pairs of CTAs on one tile (`tcgen05.mma.cta_group::2`): 1 where
     the library's rule expects them to be faster, 0 never, 2 wherever they can (tests and measurements), -1 as the

@@ -115,6 +115,10 @@ class GatedUnit(FeedForward):
     def forward(self, h, stream, step) -> None:
         if self.act == ops.GLU_SILU:  # the contraction's own epilogue
             act = self.rt.linear(h, self.w_gate_up, epilogue=ops.EPI_SWIGLU)
+        elif h.dtype == torch.bfloat16 and ops.gemm_tc_supported(h, self.w_gate_up):
+            # the unit is the contraction's epilogue, from the 32-bit sums (as SwiGLU is in the `swiglu` part)
+            act = self.rt.empty(h.shape[0], self.inner)
+            ops.gemm_tc_glu_act(h, self.w_gate_up, act, self.act, self.rt.err)
         else:
             gu = self.rt.linear(h, self.w_gate_up)
             act = self.rt.empty(h.shape[0], self.inner)
