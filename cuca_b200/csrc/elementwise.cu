@@ -563,18 +563,31 @@ CUCA_API int cuca_glu_act(const void* gu, void* out, int dtype, int n_rows, int 
 
 // ---------------------------------------------------------------- one gate per head
 // a[r, h dv + j] *= sigmoid(gate[r, h]) for every head h of dv values; a: rows of stride lda, gate: rows of stride ldg.
-template <typename T>
+// VEC values (16 bytes of bfloat16, or one 32-bit value) a thread at a time; a run of VEC values lies within one head.
+template <typename T, int VEC>
 __global__ void head_gate_kernel(T* __restrict__ a, int lda, const T* __restrict__ gate, int ldg, int n_rows, int H,
                                  int dv) {
   pdl_trigger();
   pdl_wait();
-  const size_t total = (size_t)n_rows * H * dv;
+  const int per_row = H * dv / VEC;
+  const size_t total = (size_t)n_rows * per_row;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t r = i / ((size_t)H * dv);
-    const int c = (int)(i % ((size_t)H * dv));
-    const float g = to_f32(gate[r * ldg + c / dv]);
+    const size_t r = i / per_row;
+    const int c = (int)(i % per_row) * VEC;
+    const float g = 1.f / (1.f + expf(-to_f32(gate[r * ldg + c / dv])));
     T* at = a + r * lda + c;
-    *at = from_f32<T>(to_f32(*at) / (1.f + expf(-g)));
+    if (VEC == 8) {
+      uint4 w = *reinterpret_cast<const uint4*>(at);
+      __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        h2[e] = __floats2bfloat162_rn(f.x * g, f.y * g);
+      }
+      *reinterpret_cast<uint4*>(at) = w;
+    } else {
+      *at = from_f32<T>(to_f32(*at) * g);
+    }
   }
 }
 
@@ -582,14 +595,18 @@ CUCA_API int cuca_head_gate(void* a, int lda, const void* gate, int ldg, int dty
                             cudaStream_t stream) {
   const size_t total = (size_t)n_rows * H * dv;
   if (total == 0) return 0;
-  size_t blocks = (total + 255) / 256;
+  const bool wide = dtype == CUCA_BF16 && dv % 8 == 0 && lda % 8 == 0 && ((uintptr_t)a & 15) == 0;
+  size_t blocks = (total / (wide ? 8 : 1) + 255) / 256;
   blocks = blocks > 16384 ? 16384 : blocks;
   if (dtype == CUCA_F32)
-    cuca_launch(head_gate_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, true, (float*)a, lda,
+    cuca_launch(head_gate_kernel<float, 1>, dim3((unsigned)blocks), dim3(256), 0, stream, true, (float*)a, lda,
                 (const float*)gate, ldg, n_rows, H, dv);
+  else if (dtype == CUCA_BF16 && wide)
+    cuca_launch(head_gate_kernel<__nv_bfloat16, 8>, dim3((unsigned)blocks), dim3(256), 0, stream, true,
+                (__nv_bfloat16*)a, lda, (const __nv_bfloat16*)gate, ldg, n_rows, H, dv);
   else if (dtype == CUCA_BF16)
-    cuca_launch(head_gate_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, true, (__nv_bfloat16*)a,
-                lda, (const __nv_bfloat16*)gate, ldg, n_rows, H, dv);
+    cuca_launch(head_gate_kernel<__nv_bfloat16, 1>, dim3((unsigned)blocks), dim3(256), 0, stream, true,
+                (__nv_bfloat16*)a, lda, (const __nv_bfloat16*)gate, ldg, n_rows, H, dv);
   else
     CUCA_REQUIRE(false, "head_gate: unknown dtype %d", dtype);
   CUCA_CHECK_LAUNCH("head_gate");

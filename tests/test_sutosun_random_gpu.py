@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 def random_config(seed: int) -> dict:
     rs = np.random.default_rng(2000 + seed)
     pick = lambda xs: xs[int(rs.integers(len(xs)))]  # noqa: E731
-    width = pick([24, 40, 64, 72, 96, 128, 200, 256])
+    width = pick([24, 36, 40, 52, 64, 72, 96, 100, 128, 200, 256])
     n_layers = int(rs.integers(2, 8))
     layers, mlps, borrow = [], [], {}
     for i in range(n_layers):
@@ -48,10 +48,10 @@ def random_config(seed: int) -> dict:
         if kind < 0.15:
             mlps.append(None)
         elif kind < 0.45:
-            mlps.append(su.dense(int(rs.integers(2, 40)) * 8))
+            mlps.append(su.dense(int(rs.integers(2, 40)) * pick([8, 8, 4, 6])))
         else:
             experts = pick([1, 2, 3, 4, 8, 16, 33])
-            mlps.append(su.moe(ff=pick([8, 16, 24, 40, 64, 96]), experts=experts,
+            mlps.append(su.moe(ff=pick([8, 12, 16, 20, 24, 40, 64, 96]), experts=experts,
                                top=int(rs.integers(1, min(experts, 6) + 1))))
     for i in range(n_layers):  # some entries run with another entry's tensors, an earlier or a later one
         others = [j for j in range(n_layers) if j != i and j not in borrow and i not in borrow.values()]
