@@ -138,6 +138,18 @@ class Oracle:
             self._cache[rid] = plain_sutosun.forward(self.cfg, self.w, tokens)
         return self._cache[rid]
 
+    def rounded(self, rid: str, tokens: list) -> np.ndarray:
+        """The plain implementation's logits with everything that enters a contraction, and what the caches hold,
+        rounded to bfloat16."""
+        key = ("rounded", rid)
+        if key not in self._cache:
+            plain_sutosun.ROUND = bf16_round
+            try:
+                self._cache[key] = plain_sutosun.forward(self.cfg, self.w, tokens)
+            finally:
+                plain_sutosun.ROUND = None
+        return self._cache[key]
+
     def tolerance(self, dtype: str, requests: dict) -> float:
         """What a replay may differ by, relative to a row's largest logit. 32-bit: a fixed small number. bfloat16:
         three times what rounding alone does to these very requests (the plain implementation run once more with
@@ -146,15 +158,39 @@ class Oracle:
             return 1e-4
         errs = []
         for rid, tokens in requests.items():
-            key = ("rounded", rid)
-            if key not in self._cache:
-                plain_sutosun.ROUND = bf16_round
-                try:
-                    self._cache[key] = plain_sutosun.forward(self.cfg, self.w, tokens)
-                finally:
-                    plain_sutosun.ROUND = None
             exact = self.logits(rid, tokens)
-            errs.append(np.abs(self._cache[key] - exact).max(axis=1) / np.abs(exact).max(axis=1))
+            errs.append(np.abs(self.rounded(rid, tokens) - exact).max(axis=1) / np.abs(exact).max(axis=1))
         # the median row: a routed layer takes another expert here and there once its input is rounded, and such a
         # row's error says nothing about rounding
         return max(3e-2, 3.0 * float(np.median(np.concatenate(errs))) * 2.0)
+
+
+def compare(steps, got, requests, oracle, dtype, allow=0.10, tol32=None):
+    """`replay_util.compare` for a model with routed layers. 32-bit: every wanted place within the tolerance of the
+    plain implementation. bfloat16: a token whose router logits nearly tie at the cut may go to another expert once its
+    input is rounded, and what it then leaves in the states and keys moves the tokens after it; the plain
+    implementation with rounded inputs takes the same turn. So a place is measured against the exact logits and against
+    the rounded ones and the smaller distance counts; up to `allow` of the places may still be over the tolerance (a
+    tie that falls the other way) while the median place stays well inside it, and never by a non-finite value."""
+    import replay_util as ru
+    tol = oracle.tolerance(dtype, requests)
+    if dtype == "float32":
+        return ru.compare(steps, got, requests, oracle, tol32 or tol)
+    pos = {rid: 0 for rid in requests}
+    errs = []
+    for s in steps:
+        row = 0
+        for e in s["entries"]:
+            rid = e["id"]
+            ref, near = oracle.logits(rid, requests[rid]), oracle.rounded(rid, requests[rid])
+            for w in e.get("want", []):
+                p, g = pos[rid] + w, got[s["step"]][row]
+                assert np.isfinite(g).all(), (s["step"], rid)
+                scale = float(np.abs(ref[p]).max())
+                errs.append((min(float(np.abs(g - ref[p]).max()), float(np.abs(g - near[p]).max())) / scale, s["step"], rid, p))
+                row += 1
+            pos[rid] += len(e["tokens"])
+    over = [x for x in errs if x[0] > tol]
+    assert len(over) <= max(1, allow * len(errs)), f"{len(over)} of {len(errs)} places over {tol:.2e}; first: {over[:3]}"
+    assert float(np.median([x[0] for x in errs])) < 0.5 * tol
+    return max(x[0] for x in errs)

@@ -8,7 +8,6 @@ import torch
 import plain_sutosun as ps
 import replay_util as ru
 import sutosun_util as su
-from pudinex_util import compare
 from test_bananex_gpu import CUTS, _load, _run_cut
 
 pytestmark = pytest.mark.gpu
@@ -534,7 +533,7 @@ def test_whole_and_decoded_one_by_one(models, name, dtype):
     reqs = _requests(name, cfg)
     for steps in (ru.trace_whole(reqs), ru.trace_tail_one_by_one(reqs, tail=48)):
         got = ru.run_in_process(folder, dtype, steps, ru.peak_tokens(steps), block_size=8)
-        compare(steps, got, reqs, oracle, dtype)
+        su.compare(steps, got, reqs, oracle, dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -545,7 +544,7 @@ def test_portions_down_to_two_tokens(models, name, dtype):
     for sizes in ((5, 2, 17, 3, 2, 32, 7, 2, 64, 11), (2, 2, 3, 1, 1, 8, 9, 40)):
         steps = ru.trace_portions(reqs, sizes=sizes)
         got = ru.run_in_process(folder, dtype, steps, ru.peak_tokens(steps), block_size=16)
-        compare(steps, got, reqs, oracle, dtype)
+        su.compare(steps, got, reqs, oracle, dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -559,7 +558,7 @@ def test_mixed_batches_reuse_pages_and_slots(models, name, dtype):
     for live, pools in ((4, "full"), (3, "sized")):
         steps = ru.trace_mixed(reqs, max_live=live, seed=7 + live)
         got = ru.run_in_process(folder, dtype, steps, ru.peak_tokens(steps), block_size=8, window_pools=pools)
-        compare(steps, got, reqs, oracle, dtype)
+        su.compare(steps, got, reqs, oracle, dtype)
 
 
 def test_32_bit_hardly_depends_on_cuts_or_company(models):
@@ -592,7 +591,7 @@ def test_long_decoding(models):
     steps = ru.trace_tail_one_by_one(reqs, tail=200)
     for dtype in ("float32", "bfloat16"):
         got = ru.run_in_process(folder, dtype, steps, ru.peak_tokens(steps), block_size=8, window_pools="sized")
-        compare(steps, got, reqs, oracle, dtype)
+        su.compare(steps, got, reqs, oracle, dtype)
 
 
 def test_long_prompts(models):
@@ -601,7 +600,7 @@ def test_long_prompts(models):
     for steps in (ru.trace_whole(reqs), ru.trace_portions(reqs, sizes=(7, 300, 2, 280, 1, 64))):
         for dtype in ("bfloat16", "float32"):
             got = ru.run_in_process(folder, dtype, steps, ru.peak_tokens(steps), block_size=16)
-            compare(steps, got, reqs, oracle, dtype)
+            su.compare(steps, got, reqs, oracle, dtype)
 
 
 def test_trace_run_as_a_program(models):
@@ -609,7 +608,7 @@ def test_trace_run_as_a_program(models):
     reqs = _requests("one", cfg)
     steps = ru.trace_mixed(reqs, max_live=4, seed=1)
     got = ru.run_subprocess(folder, "float32", steps, ru.peak_tokens(steps))
-    compare(steps, got, reqs, oracle, "float32")
+    su.compare(steps, got, reqs, oracle, "float32")
 
 
 # ------------------------------------------------------------------------------------------ the entry point

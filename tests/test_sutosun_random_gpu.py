@@ -6,7 +6,6 @@ import pytest
 
 import replay_util as ru
 import sutosun_util as su
-from pudinex_util import compare
 
 pytestmark = pytest.mark.gpu
 
@@ -73,4 +72,4 @@ def test_random_configuration(tmp_path, seed):
                       ru.trace_portions(reqs, sizes=(7, 2, 33, 2, 3, 64, 5)),
                       ru.trace_mixed(reqs, max_live=4, seed=seed)):
             got = ru.run_in_process(folder, dtype, steps, ru.peak_tokens(steps), block_size=16)
-            compare(steps, got, reqs, oracle, dtype, tol32=3e-4)
+            su.compare(steps, got, reqs, oracle, dtype, tol32=3e-4)
