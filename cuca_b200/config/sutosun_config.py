@@ -90,8 +90,6 @@ class RetentionConfig:
         _positive(where, heads=c.heads, dim=c.dim, vdim=c.vdim)
         if len(c.decay) != c.heads:
             raise ConfigError(f"config.json `{where}.decay` has {len(c.decay)} entries for {c.heads} heads")
-        if c.rot is not None and c.rot.yarn is not None:
-            raise ConfigError(f"config.json `{where}.rot.scaling`: retention rotates with plain frequencies")
         return c
 
 

@@ -331,6 +331,37 @@ def test_the_sink_takes_the_weight_when_it_is_large(dtype, dim, vdim):
         assert np.abs(got - want).max() < (2e-5 if dtype == torch.float32 else 3e-2) * np.abs(want).max()
 
 
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("splits, cluster", [(1, True), (2, True), (3, True), (4, False), (8, True), (16, False)])
+def test_stored_sink_scores_in_every_merge_of_the_split_key_decode(monkeypatch, dim, splits, cluster):
+    """Single tokens over 1,100 keys with the keys dealt to 1 to 16 chunks, merged inside one block, through a
+    cluster's shared memory or by the last block to arrive: the sink's term goes in once wherever the row's sum is
+    closed. A sink of the planted score's size takes half the weight, so a sink counted per chunk, or not at all, shows."""
+    from cuca_b200.cache.device import CacheView
+    from cuca_b200.kernels import ops
+    monkeypatch.setenv("CUCA_DECODE_SPLITS", str(splits))
+    monkeypatch.setattr(ops, "CLUSTER_MERGE", cluster)
+    n, far, bs, dtype = 1100, 700, 16, torch.bfloat16
+    rt, part, m, ws, x, E, eps = _planted(dtype, dim, dim, n, far, slice(n - 6, n), target=9.0, sink=9.0, every=5000)
+    dev = rt.device
+    want = ps.gated_attention(x, ws, "l0.mix.", m, eps)
+    lost = ps.gated_attention(x, dict(ws, **{"l0.mix.sink": ws["l0.mix.sink"] - 30.0}), "l0.mix.", m, eps)
+    assert np.abs(want[-1] - lost[-1]).max() > 0.2 * np.abs(want[-1]).max()
+    rs = np.random.default_rng(splits)
+    kpool = torch.zeros((80, 1, bs, dim), dtype=dtype, device=dev)
+    vpool = torch.zeros((80, 1, bs, dim), dtype=dtype, device=dev)
+    tables = torch.full((4, 72), -1, dtype=torch.int32, device=dev)
+    tables[1, :70] = torch.tensor(rs.permutation(80)[:70].tolist(), dtype=torch.int32)
+
+    def fwd(h, step):
+        stream = rt.stream(torch.zeros(h.shape[0], E, device=dev))
+        part.forward(h.to(dtype), stream, step, CacheView(kpool, vpool, tables, bs, 0, None, step.slots))
+        return stream.data
+    got = _run_cut(dev, fwd, [x], [[n - 8] + [1] * 8], [1], E)[0]
+    assert np.abs(got - want)[n - 8:].max() < 3e-2 * np.abs(want).max()
+    assert int(rt.err.item()) == 0
+
+
 LATENTS = [su.lat(), su.lat(heads=5, dim=4, rot_dim=0, vdim=36, kv_rank=8), su.lat(heads=1, dim=24, rot_dim=16, vdim=8, kv_rank=16, scale=0.3, rotated=False),
            su.lat(heads=4, dim=32, rot_dim=16, vdim=48, kv_rank=64, base=250000.0,
                   scaling={"factor": 16.0, "original": 32, "fast": 8.0, "slow": 1.0}),
