@@ -8,10 +8,13 @@
 //   warp w takes keys 16 w .. 16 w + 15: S = Q K^T over Dk, scale, per-row window and causal mask;
 //   the row maximum over the four warps goes through shared memory; P = exp2(S - max) is written as bfloat16;
 //   warp w owns rank / 4 of the output columns: O[:, its columns] = O * corr + P V with V the same shared tile.
+// Portions of prompts with two heads or more run two heads to a CTA of eight warps over the same key tiles, copied into
+// two buffers in turn (`latent_attention_pair_kernel`).
 // Row sums are kept per thread and added up at the end. The plain kernel (latent_attention.cu) serves the 32-bit
 // path and the sizes this one refuses (Dk not a multiple of 16, rank not a multiple of 32 or above 512).
 #include "common.cuh"
 #include <math.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -27,6 +30,7 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -312,6 +316,218 @@ latent_attention_mma_kernel(Params p) {
   }
 }
 
+// Portions of prompts, two heads per CTA: eight warps, warps 0-3 take head 2 y and warps 4-7 head 2 y + 1 of the same
+// 16 tokens, each four as in the kernel above. Both heads read the same key tiles, and the tiles go into two buffers in
+// turn, so tile t + 1 is on its way while tile t is worked on: half the traffic from L2 per head and no wait for a
+// whole tile between two tiles' arithmetic. The arithmetic of a row (tile order, sums) is the kernel's above.
+template <int NT8>
+__global__ void __launch_bounds__(256)
+latent_attention_pair_kernel(Params p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int RS = p.Dk + PAD;
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);               // [2 heads][16][RS]
+  bf16* Ks = Qs + 2 * 16 * RS;                                 // [2 buffers][KT][RS]
+  bf16* Ps = Ks + 2 * KT * RS;                                 // [2 heads][16][PS]
+  float* wmax = reinterpret_cast<float*>(Ps + 2 * 16 * PS);    // [2 heads][4][16]
+  float* wsum = wmax + 128;                                    // [2 heads][4][16]
+  pdl_trigger();
+  pdl_wait();
+  const int grp = threadIdx.x >> 7, tid = threadIdx.x & 127;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int row0 = p.tile_row0[blockIdx.x];
+  int nrows = p.tile_nrows[blockIdx.x];
+  const int seq = p.seq_of_row[row0];
+  if (seq < 0 || nrows <= 0) return;  // (the same for every thread of the block)
+  if (nrows > 16) nrows = 16;
+  const int head = blockIdx.y * 2 + grp;
+  const bool head_ok = head < p.H;
+  const int P0 = p.positions[row0];
+  const int Pmax = P0 + nrows - 1;
+  const int lo_tile = (p.window > 0 && P0 - (p.window - 1) > 0) ? P0 - (p.window - 1) : 0;
+  const int H = p.H, Dk = p.Dk, rank = p.rank;
+  bf16* Qg = Qs + grp * 16 * RS;
+  bf16* Pg = Ps + grp * 16 * PS;
+  float* wmaxg = wmax + grp * 64;
+  float* wsumg = wsum + grp * 64;
+
+  for (int e = tid; e < 16 * Dk; e += 128) {  // this head's queries, as bfloat16
+    const int r = e / Dk, i = e - r * Dk;
+    float v = 0.f;
+    if (r < nrows && head_ok) v = p.qk[((size_t)(row0 + r) * H + head) * Dk + i];
+    Qg[r * RS + i] = __float2bfloat16_rn(v);
+  }
+  int Pr[2], lor[2];
+  bool rvalid[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = g + 8 * i;
+    rvalid[i] = r < nrows && head_ok;
+    Pr[i] = P0 + r;
+    lor[i] = (p.window > 0 && Pr[i] - (p.window - 1) > 0) ? Pr[i] - (p.window - 1) : 0;
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float acc[NT8][4];
+#pragma unroll
+  for (int i = 0; i < NT8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  const int DW = rank >> 2;
+  const int ntiles = DW >> 3;
+  const int* table = p.tables + (size_t)seq * p.table_stride;
+  const int chunks = Dk >> 3;
+  const uint32_t qs_addr = smem_u32(Qg), ks_addr = smem_u32(Ks), ps_addr = smem_u32(Pg);
+  const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+  const int b_key = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
+  const int v_key = (lane & 7) + ((lane >> 3) & 1) * 8, v_col = (lane >> 4) * 8;
+
+  // four threads per key: one page lookup each, then the row's 16-byte pieces in turn
+  auto load_tile = [&](int kt, int buf) {
+    const int j = threadIdx.x >> 2;
+    const int kp = kt + j;
+    bool valid = kp >= lo_tile && kp <= Pmax;
+    const bf16* src = p.pool;
+    if (valid) {
+      const int blk = table[kp / p.bs];
+      if (blk < 0 || blk >= p.n_blocks) {
+        if (p.err) atomicExch(p.err, CUCA_ERR_BLOCK_RANGE);
+        valid = false;
+      } else {
+        src = p.pool + ((size_t)blk * p.bs + (kp % p.bs)) * Dk;
+      }
+    }
+    const uint32_t dst = ks_addr + (uint32_t)((buf * KT + j) * RS) * 2;
+    for (int ch = threadIdx.x & 3; ch < chunks; ch += 4) cp_async16(dst + ch * 16, valid ? src + ch * 8 : p.pool, valid);
+    cp_async_commit();
+  };
+
+  const int kt_first = (lo_tile / KT) * KT;
+  load_tile(kt_first, 0);
+  int buf = 0;
+  for (int kt = kt_first; kt <= Pmax; kt += KT, buf ^= 1) {
+    if (kt + KT <= Pmax) {
+      load_tile(kt + KT, buf ^ 1);  // (that buffer was read to the end before the barrier that closed the last round)
+      cp_async_wait_but_one();
+    } else {
+      cp_async_wait_all();
+    }
+    __syncthreads();  // tile kt is there for every thread (and, the first time, the queries are written)
+    const uint32_t kb = ks_addr + (uint32_t)(buf * KT * RS) * 2;
+
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+    for (int k0 = 0; k0 < Dk; k0 += 16) {
+      uint32_t a[4], b[4];
+      ldsm_x4(a, qs_addr + (uint32_t)(a_row * RS + k0 + a_col) * 2);
+      ldsm_x4(b, kb + (uint32_t)((warp * 16 + b_key) * RS + k0 + b_col) * 2);
+      mma_bf16(s[0], a, b[0], b[1]);
+      mma_bf16(s[1], a, b[2], b[3]);
+    }
+    const int kbase = kt + warp * 16 + 2 * t;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = j >> 1;
+        const int kp = kbase + nt * 8 + (j & 1);
+        const bool ok = rvalid[i] && kp >= lor[i] && kp <= Pr[i];
+        s[nt][j] = ok ? s[nt][j] * p.scale_log2 : -INFINITY;
+        mx[i] = fmaxf(mx[i], s[nt][j]);
+      }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+    }
+    if (t == 0) {
+      wmaxg[warp * 16 + g] = mx[0];
+      wmaxg[warp * 16 + g + 8] = mx[1];
+    }
+    __syncthreads();
+    float corr[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = g + 8 * i;
+      const float tm = fmaxf(fmaxf(wmaxg[r], wmaxg[16 + r]), fmaxf(wmaxg[32 + r], wmaxg[48 + r]));
+      const float mn = fmaxf(m[i], tm);
+      corr[i] = (mn == -INFINITY) ? 1.f : exp2f(m[i] - mn);
+      m[i] = mn;
+    }
+    float ps[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      float pv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = j >> 1;
+        pv[j] = (m[i] == -INFINITY) ? 0.f : exp2f(s[nt][j] - m[i]);
+        ps[i] += pv[j];
+      }
+      const int col = warp * 16 + nt * 8 + 2 * t;
+      *reinterpret_cast<uint32_t*>(Pg + g * PS + col) = pack_bf16(pv[0], pv[1]);
+      *reinterpret_cast<uint32_t*>(Pg + (g + 8) * PS + col) = pack_bf16(pv[2], pv[3]);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) l[i] = l[i] * corr[i] + ps[i];
+#pragma unroll
+    for (int n = 0; n < NT8; ++n) {
+      acc[n][0] *= corr[0];
+      acc[n][1] *= corr[0];
+      acc[n][2] *= corr[1];
+      acc[n][3] *= corr[1];
+    }
+    __syncthreads();  // P of this head's four warps is written
+
+#pragma unroll
+    for (int kk = 0; kk < KT / 16; ++kk) {
+      uint32_t a[4];
+      ldsm_x4(a, ps_addr + (uint32_t)(a_row * PS + kk * 16 + a_col) * 2);
+#pragma unroll
+      for (int np = 0; np < NT8 / 2; ++np) {
+        if (2 * np < ntiles) {
+          const bool second = 2 * np + 1 < ntiles;
+          const int col = warp * DW + np * 16 + (second ? v_col : 0);
+          uint32_t b[4];
+          ldsm_x4_trans(b, kb + (uint32_t)((kk * 16 + v_key) * RS + col) * 2);
+          mma_bf16(acc[2 * np], a, b[0], b[1]);
+          if (second) mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();  // the tile, the maxima and P are read to the end: the next round may overwrite them
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+  if (t == 0) {
+    wsumg[warp * 16 + g] = l[0];
+    wsumg[warp * 16 + g + 8] = l[1];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (!rvalid[i]) continue;
+    const int r = g + 8 * i;
+    float L = wsumg[r] + wsumg[16 + r] + wsumg[32 + r] + wsumg[48 + r];
+    if (p.sink && m[i] != -INFINITY) L += exp2f(p.sink[head] * 1.4426950408889634f - m[i]);  // (m in log2 units)
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    float* o = p.out + ((size_t)(row0 + r) * H + head) * rank + warp * DW;
+#pragma unroll
+    for (int n = 0; n < NT8; ++n) {
+      if (n < ntiles) {
+        o[n * 8 + 2 * t] = acc[n][2 * i] * inv;
+        o[n * 8 + 2 * t + 1] = acc[n][2 * i + 1] * inv;
+      }
+    }
+  }
+}
+
 // One block per (group, head block, row of 16): out = sum_z acc_z 2^(m_z - M) / sum_z l_z 2^(m_z - M), z in order
 // (up to 64 splits).
 __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
@@ -379,6 +595,34 @@ int launch(const Params& p, int n_groups, int head_blocks, cudaStream_t stream) 
   return 0;
 }
 
+size_t pair_smem_bytes(int Dk) {
+  return (size_t)(2 * 16 + 2 * KT) * (Dk + PAD) * sizeof(bf16) + (size_t)2 * 16 * PS * sizeof(bf16) + 2 * 128 * sizeof(float);
+}
+
+template <int NT8>
+int launch_pair(const Params& p, int n_groups, cudaStream_t stream) {
+  const size_t smem = pair_smem_bytes(p.Dk);
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_pair_kernel<NT8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) {
+      cuca_set_error("latent_attention_mma: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+      return 2;
+    }
+    configured = smem;
+  }
+  cuca_launch(latent_attention_pair_kernel<NT8>, dim3(n_groups, (p.H + 1) / 2, 1), dim3(256), smem, stream, true, p);
+  return 0;
+}
+
+// Portions of prompts with two heads or more go two heads to a CTA where its two key buffers fit shared memory
+// (CUCA_LATENT_PAIR=0: never, a measuring aid).
+bool pair_form(const Params& p, bool portions) {
+  static const int allowed = getenv("CUCA_LATENT_PAIR") ? atoi(getenv("CUCA_LATENT_PAIR")) : 1;
+  return allowed && portions && p.H >= 2 && pair_smem_bytes(p.Dk) <= 227 * 1024;
+}
+
 }  // namespace
 
 // Whether the tensor-core form takes these sizes (the cache must be bfloat16).
@@ -413,6 +657,15 @@ CUCA_API int cuca_latent_attention_mma_s(const float* qk, float* out, const void
   CUCA_REQUIRE(head_blocks <= 65535, "latent_attention_mma: %d heads exceed the launch limit", H);
   const int ntiles = rank / 32;
   int rc;
+  if (pair_form(p, portions)) {
+    CUCA_REQUIRE((H + 1) / 2 <= 65535, "latent_attention_mma: %d heads exceed the launch limit", H);
+    if (ntiles <= 4) rc = launch_pair<4>(p, n_groups, stream);
+    else if (ntiles <= 8) rc = launch_pair<8>(p, n_groups, stream);
+    else rc = launch_pair<16>(p, n_groups, stream);
+    if (rc) return rc;
+    CUCA_CHECK_LAUNCH("latent_attention_mma");
+    return 0;
+  }
   if (ntiles <= 4) rc = launch<4>(p, n_groups, head_blocks, stream);
   else if (ntiles <= 8) rc = launch<8>(p, n_groups, head_blocks, stream);
   else rc = launch<16>(p, n_groups, head_blocks, stream);
