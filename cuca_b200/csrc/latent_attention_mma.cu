@@ -8,8 +8,8 @@
 //   warp w takes keys 16 w .. 16 w + 15: S = Q K^T over Dk, scale, per-row window and causal mask;
 //   the row maximum over the four warps goes through shared memory; P = exp2(S - max) is written as bfloat16;
 //   warp w owns rank / 4 of the output columns: O[:, its columns] = O * corr + P V with V the same shared tile.
-// Portions of prompts with two heads or more run two heads to a CTA of eight warps over the same key tiles, copied into
-// two buffers in turn (`latent_attention_pair_kernel`).
+// Portions of prompts with two heads or more run two to four heads to a CTA (four warps each) over the same key tiles,
+// copied into two buffers in turn (`latent_attention_pair_kernel`).
 // Row sums are kept per thread and added up at the end. The plain kernel (latent_attention.cu) serves the 32-bit
 // path and the sizes this one refuses (Dk not a multiple of 16, rank not a multiple of 32 or above 512).
 #include "common.cuh"
@@ -316,20 +316,21 @@ latent_attention_mma_kernel(Params p) {
   }
 }
 
-// Portions of prompts, two heads per CTA: eight warps, warps 0-3 take head 2 y and warps 4-7 head 2 y + 1 of the same
-// 16 tokens, each four as in the kernel above. Both heads read the same key tiles, and the tiles go into two buffers in
-// turn, so tile t + 1 is on its way while tile t is worked on: half the traffic from L2 per head and no wait for a
-// whole tile between two tiles' arithmetic. The arithmetic of a row (tile order, sums) is the kernel's above.
-template <int NT8>
-__global__ void __launch_bounds__(256)
+// Portions of prompts, HG heads per CTA (2 to 4): 4 HG warps, warps 4 a .. 4 a + 3 take head HG y + a of the same 16
+// tokens, each four as in the kernel above. The heads read the same key tiles, and the tiles go into two buffers in
+// turn, so tile t + 1 is on its way while tile t is worked on: 1 / HG of the traffic from L2 per head, more warps per SM
+// than one head's four, and no wait for a whole tile between two tiles' arithmetic. The arithmetic of a row (tile
+// order, sums) is the kernel's above.
+template <int NT8, int HG>
+__global__ void __launch_bounds__(128 * HG)
 latent_attention_pair_kernel(Params p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int RS = p.Dk + PAD;
-  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);               // [2 heads][16][RS]
-  bf16* Ks = Qs + 2 * 16 * RS;                                 // [2 buffers][KT][RS]
-  bf16* Ps = Ks + 2 * KT * RS;                                 // [2 heads][16][PS]
-  float* wmax = reinterpret_cast<float*>(Ps + 2 * 16 * PS);    // [2 heads][4][16]
-  float* wsum = wmax + 128;                                    // [2 heads][4][16]
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);               // [HG heads][16][RS]
+  bf16* Ks = Qs + HG * 16 * RS;                                 // [2 buffers][KT][RS]
+  bf16* Ps = Ks + 2 * KT * RS;                                 // [HG heads][16][PS]
+  float* wmax = reinterpret_cast<float*>(Ps + HG * 16 * PS);    // [HG heads][4][16]
+  float* wsum = wmax + HG * 64;                                   // [HG heads][4][16]
   pdl_trigger();
   pdl_wait();
   const int grp = threadIdx.x >> 7, tid = threadIdx.x & 127;
@@ -340,7 +341,7 @@ latent_attention_pair_kernel(Params p) {
   const int seq = p.seq_of_row[row0];
   if (seq < 0 || nrows <= 0) return;  // (the same for every thread of the block)
   if (nrows > 16) nrows = 16;
-  const int head = blockIdx.y * 2 + grp;
+  const int head = blockIdx.y * HG + grp;
   const bool head_ok = head < p.H;
   const int P0 = p.positions[row0];
   const int Pmax = P0 + nrows - 1;
@@ -381,9 +382,10 @@ latent_attention_pair_kernel(Params p) {
   const int b_key = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
   const int v_key = (lane & 7) + ((lane >> 3) & 1) * 8, v_col = (lane >> 4) * 8;
 
-  // four threads per key: one page lookup each, then the row's 16-byte pieces in turn
+  // 2 HG threads per key: one page lookup each, then the row's 16-byte pieces in turn
+  constexpr int TPK = 2 * HG;
   auto load_tile = [&](int kt, int buf) {
-    const int j = threadIdx.x >> 2;
+    const int j = threadIdx.x / TPK;
     const int kp = kt + j;
     bool valid = kp >= lo_tile && kp <= Pmax;
     const bf16* src = p.pool;
@@ -397,7 +399,7 @@ latent_attention_pair_kernel(Params p) {
       }
     }
     const uint32_t dst = ks_addr + (uint32_t)((buf * KT + j) * RS) * 2;
-    for (int ch = threadIdx.x & 3; ch < chunks; ch += 4) cp_async16(dst + ch * 16, valid ? src + ch * 8 : p.pool, valid);
+    for (int ch = threadIdx.x % TPK; ch < chunks; ch += TPK) cp_async16(dst + ch * 16, valid ? src + ch * 8 : p.pool, valid);
     cp_async_commit();
   };
 
@@ -595,32 +597,44 @@ int launch(const Params& p, int n_groups, int head_blocks, cudaStream_t stream) 
   return 0;
 }
 
-size_t pair_smem_bytes(int Dk) {
-  return (size_t)(2 * 16 + 2 * KT) * (Dk + PAD) * sizeof(bf16) + (size_t)2 * 16 * PS * sizeof(bf16) + 2 * 128 * sizeof(float);
+size_t pair_smem_bytes(int Dk, int hg) {
+  return (size_t)(hg * 16 + 2 * KT) * (Dk + PAD) * sizeof(bf16) + (size_t)hg * 16 * PS * sizeof(bf16) +
+         (size_t)hg * 128 * sizeof(float);
 }
 
-template <int NT8>
+template <int NT8, int HG>
 int launch_pair(const Params& p, int n_groups, cudaStream_t stream) {
-  const size_t smem = pair_smem_bytes(p.Dk);
+  const size_t smem = pair_smem_bytes(p.Dk, HG);
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(latent_attention_pair_kernel<NT8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_pair_kernel<NT8, HG>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
       cuca_set_error("latent_attention_mma: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
       return 2;
     }
     configured = smem;
   }
-  cuca_launch(latent_attention_pair_kernel<NT8>, dim3(n_groups, (p.H + 1) / 2, 1), dim3(256), smem, stream, true, p);
+  cuca_launch(latent_attention_pair_kernel<NT8, HG>, dim3(n_groups, (p.H + HG - 1) / HG, 1), dim3(128 * HG), smem,
+              stream, true, p);
   return 0;
 }
 
-// Portions of prompts with two heads or more go two heads to a CTA where its two key buffers fit shared memory
-// (CUCA_LATENT_PAIR=0: never, a measuring aid).
-bool pair_form(const Params& p, bool portions) {
-  static const int allowed = getenv("CUCA_LATENT_PAIR") ? atoi(getenv("CUCA_LATENT_PAIR")) : 1;
-  return allowed && portions && p.H >= 2 && pair_smem_bytes(p.Dk) <= 227 * 1024;
+// How many heads of a portion's 16 tokens share a CTA (0: the one-head kernel): as many of 4, 3, 2 as the heads and
+// shared memory allow (CUCA_LATENT_PAIR=0: never; =2, 3, 4: at most that many; a measuring aid).
+int heads_per_cta(const Params& p, bool portions) {
+  static const int most = getenv("CUCA_LATENT_PAIR") ? atoi(getenv("CUCA_LATENT_PAIR")) : 4;
+  if (!portions) return 0;
+  for (int hg = most < 4 ? most : 4; hg >= 2; --hg)
+    if (p.H >= hg && pair_smem_bytes(p.Dk, hg) <= 227 * 1024) return hg;
+  return 0;
+}
+
+template <int NT8>
+int launch_pair_by_heads(const Params& p, int hg, int n_groups, cudaStream_t stream) {
+  if (hg == 4) return launch_pair<NT8, 4>(p, n_groups, stream);
+  if (hg == 3) return launch_pair<NT8, 3>(p, n_groups, stream);
+  return launch_pair<NT8, 2>(p, n_groups, stream);
 }
 
 }  // namespace
@@ -657,11 +671,11 @@ CUCA_API int cuca_latent_attention_mma_s(const float* qk, float* out, const void
   CUCA_REQUIRE(head_blocks <= 65535, "latent_attention_mma: %d heads exceed the launch limit", H);
   const int ntiles = rank / 32;
   int rc;
-  if (pair_form(p, portions)) {
-    CUCA_REQUIRE((H + 1) / 2 <= 65535, "latent_attention_mma: %d heads exceed the launch limit", H);
-    if (ntiles <= 4) rc = launch_pair<4>(p, n_groups, stream);
-    else if (ntiles <= 8) rc = launch_pair<8>(p, n_groups, stream);
-    else rc = launch_pair<16>(p, n_groups, stream);
+  if (const int hg = heads_per_cta(p, portions)) {
+    CUCA_REQUIRE((H + hg - 1) / hg <= 65535, "latent_attention_mma: %d heads exceed the launch limit", H);
+    if (ntiles <= 4) rc = launch_pair_by_heads<4>(p, hg, n_groups, stream);
+    else if (ntiles <= 8) rc = launch_pair_by_heads<8>(p, hg, n_groups, stream);
+    else rc = launch_pair_by_heads<16>(p, hg, n_groups, stream);
     if (rc) return rc;
     CUCA_CHECK_LAUNCH("latent_attention_mma");
     return 0;
